@@ -1,0 +1,69 @@
+"""ctypes binding of the C ABI declared in include/nestquant_b200.h.
+
+The library is built in-tree by `python -m nestquant_b200.build`.  There is no fallback: if the shared object is
+missing or fails to load, importing a symbol from here raises, and every compute entry point needs a CUDA device.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libnestquant_b200.so")
+
+NQ_OK, NQ_ERR_ARG, NQ_ERR_CUDA, NQ_ERR_UNSUPPORTED = 0, -1, -2, -3
+TABLE_WIDTH = 20
+MAX_TOKENS = 32
+MAX_PICKS = 256
+
+_p, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/nestquant_b200.h one to one
+SIGNATURES = {
+    "nq_last_error": (C.c_char_p, []),
+    "nq_build_arch": (_i, []),
+    "nq_rk_codes": (_i, [C.POINTER(_i64)]),
+    "nq_bk_codes": (_i, [C.POINTER(_i64)]),
+    "nq_plane_bytes": (_sz, [_sz, _i]),
+    "nq_pf_decode": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "nq_mailbox": (_i, [_p, _p, _p, _p, _p, _i, _p]),
+}
+
+_lib = None
+
+
+class NestQuantError(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded shared library (loads on first use; raises if it has not been built)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise NestQuantError(f"{LIB_PATH} is missing: run `python -m nestquant_b200.build` (needs nvcc); "
+                                 "there is no CPU or PyTorch fallback for this path")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            f = getattr(L, name)        # AttributeError here = header and library out of sync
+            f.restype, f.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def check(rc, what=""):
+    if rc != NQ_OK:
+        msg = lib().nq_last_error()
+        raise NestQuantError(f"{what or 'nestquant_b200'} failed ({rc}): {msg.decode() if msg else ''}")
+
+
+def ptr(t):
+    """data pointer of a torch tensor (or None / int passthrough)"""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t or None
+    return t.data_ptr()
+
+
+def current_stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream

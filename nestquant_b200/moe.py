@@ -1,0 +1,309 @@
+"""Host side of the NestQuant MoE layer on B200: plane generators, device table rows, the layer object and the mailbox.
+
+Mirrors the operator surface of the reference's sm120/moe.py (same class and function names, argument meaning and
+error behaviour) so scripts written against it run unchanged:
+  RKP / rbits / proj_sizes / make_flags / pack_words / unpack_words   sm120/moe.py:10-63
+  Proj, Expert, entry                                                  sm120/moe.py:76-107,174-229
+  MoELayer (.set / __call__ / .prefill), Mailbox                       sm120/moe.py:231-342
+Everything that computes runs in the CUDA library behind nestquant_b200.ext; there is no torch or CPU fallback here
+(the dense reference decode of the original module lives in the test oracle, not in this package).
+"""
+import math
+
+import torch
+
+from . import ext as _ext
+
+TBL_W = 20
+
+# window pattern per code: step p of a ring is KA + ((MASK >> (p % 16)) & 1) bits wide
+RKP = {0: (2, 0x0000), 1: (1, 0xEEEE), 2: (2, 0xAAAA), 3: (2, 0x8888), 4: (3, 0x0000), 5: (1, 0xAAAA),
+       6: (1, 0xFFFE), 7: (2, 0x9248), 8: (1, 0xFEFE), 9: (2, 0xD5AA)}
+RK_OF = {2: 0, 1.75: 1, 2.5: 2, 2.25: 3, 3: 4, 1.5: 5, 1.9375: 6, 2.3125: 7, 1.875: 8, 2.5625: 9}
+
+
+def popc(m):
+    return bin(m).count("1")
+
+
+def rbits(rk):
+    """bits of one lane record (64 weights) for window code rk"""
+    ka, mask = RKP[rk]
+    return 4 * (16 * ka + popc(mask))
+
+
+def split_bits(bits):
+    """pieces of a record in the sub-array layout: (#128-bit, has 64, has 32, has 16, tail bits)"""
+    r = bits % 128
+    return bits // 128, (r >> 6) & 1, (r >> 5) & 1, (r >> 4) & 1, bits % 16
+
+
+def proj_sizes(N, K, nm=None, rk=0, bk=0):
+    """bytes per plane of an N x K projection; nm = flagged chunks per strip in mask mode (None = every chunk refined)"""
+    S, C = N // 16, K // 128
+    R = C if nm is None else nm
+    plane = lambda nrec, code: nrec * rbits(code) // 8 + (4 if rbits(code) % 16 else 0)
+    return dict(S=S, C=C, nm=nm, rk=rk, bk=bk, base=plane(S * C * 32, bk), p4=plane(S * R * 32, rk), d4=S * R * 4,
+                flags=0 if nm is None else S * 8, nrec_r=S * R * 32)
+
+
+def make_flags(S, C, nm, gen, grp=8):
+    """nm flagged chunks per strip, identical over each group of `grp` strips -> (int64 [S], bool [S, C])"""
+    ng = (S + grp - 1) // grp
+    pick = torch.rand(ng, C, generator=gen).argsort(1)[:, :nm]
+    fl = torch.zeros(ng, C, dtype=torch.bool)
+    fl.scatter_(1, pick, True)
+    fl = fl.repeat_interleave(grp, 0)[:S]
+    return (fl.long() << torch.arange(C)).sum(1), fl
+
+
+def _pieces(bits):
+    """(stream bit offset, width) of each sub-array of a record, in storage order"""
+    n4, n2, n1, nh, T = split_bits(bits)
+    out, o = [], 0
+    if n4:
+        out.append((0, 128 * n4)); o = 128 * n4
+    for has, w in ((n2, 64), (n1, 32), (nh, 16)):
+        if has:
+            out.append((o, w)); o += w
+    if T:
+        out.append((o, T))
+    return out
+
+
+def _to_bits(words, bits):
+    """int64 [nrec, nw] of uint32 values -> uint8 {0,1} [nrec, bits], LSB first"""
+    sh = torch.arange(32, device=words.device)
+    return ((words[:, :, None] >> sh) & 1).to(torch.uint8).reshape(words.shape[0], -1)[:, :bits]
+
+
+def _bits_to_bytes(b):
+    b = b.reshape(-1)
+    pad = (-b.numel()) % 8
+    if pad:
+        b = torch.cat([b, b.new_zeros(pad)])
+    w = (b.view(-1, 8).to(torch.int32) << torch.arange(8, device=b.device, dtype=torch.int32)).sum(1)
+    return w.to(torch.uint8)
+
+
+def pack_words(w, bits):
+    """w: int64 [nrec, nw] record words (uint32 values) -> int32 tensor holding the sub-array layout of the plane.
+    Each piece of the record is stored contiguously over all records; the tail (bits % 16 bits per record) is
+    bit-packed across records and followed by a 4-byte pad."""
+    b = _to_bits(w, bits)
+    parts = [_bits_to_bytes(b[:, o:o + n].contiguous()) for o, n in _pieces(bits)]
+    if bits % 16:
+        parts.append(torch.zeros(4, dtype=torch.uint8, device=w.device))
+    out = torch.cat(parts)
+    assert out.numel() % 4 == 0, "record count must keep the plane word-aligned (a multiple of 32 records does)"
+    return out.view(torch.int32)
+
+
+def unpack_words(t, nrec, bits):
+    """inverse of pack_words -> int64 [nrec, nw]"""
+    by = t.contiguous().view(torch.uint8)
+    allbits = ((by[:, None].to(torch.int32) >> torch.arange(8, device=t.device, dtype=torch.int32)) & 1).reshape(-1)
+    nw = (bits + 31) // 32
+    rec = torch.zeros(nrec, nw * 32, dtype=torch.int64, device=t.device)
+    pos = 0
+    for o, n in _pieces(bits):
+        rec[:, o:o + n] = allbits[pos:pos + nrec * n].view(nrec, n)
+        pos += (nrec * n + 7) // 8 * 8
+    return (rec.view(nrec, nw, 32) << torch.arange(32, device=t.device)).sum(-1)
+
+
+_MBN = None
+
+
+def all_MbN():
+    """every valid block word: 1 <= Mb <= 255, 0 <= N <= 255, Mb + N <= 257"""
+    global _MBN
+    if _MBN is None:
+        _MBN = torch.tensor([(m, n) for m in range(1, 256) for n in range(0, min(255, 257 - m) + 1)])
+    return _MBN
+
+
+class Proj:
+    """Seeded random packed planes of one N x K projection of one expert.
+
+    base  int32 [S*C*32*4]   one 128-bit record per lane
+    p4    int32 view of the residual plane in the sub-array layout (+ 4 B pad when the record has a bit tail)
+    d4    int32 [S*R]        block word Mb | N << 8 per refined unit
+    var   uint8 [S*C] or None: bit g negates ring g.   flags int64 [S] or None (mask mode, nm flagged chunks/strip)
+    mbn   'rand' (Mb in [120,255], N ~ U(0,0.8) Mb, 5 % drawn from the whole valid range) or ('exh', offset) to walk
+          every valid block word.
+    """
+
+    def __init__(s, N, K, gen, nm=None, rk=0, mbn="rand", var=False, bk=0):
+        if bk != 0:
+            raise NotImplementedError("only the 128-bit ring base (base code 0) is built into the kernels")
+        z = proj_sizes(N, K, nm, rk, bk)
+        s.z, s.N, s.K, s.rk, s.bk = z, N, K, rk, bk
+        S, C = z["S"], z["C"]
+        R = C if nm is None else nm
+        dev = gen.device
+        s.base = torch.randint(-2**31, 2**31 - 1, (S * C * 32 * 4,), generator=gen, dtype=torch.int32, device=dev)
+        nb = z["p4"]
+        raw = torch.randint(0, 256, ((nb + 3) // 4 * 4,), generator=gen, dtype=torch.uint8, device=dev)
+        if rbits(rk) % 16:
+            raw[nb - 4:] = 0
+        s.p4 = raw.view(torch.int32)
+        nu = S * R
+        if mbn == "rand":
+            Mb = torch.randint(120, 256, (nu,), generator=gen, device=dev)
+            Nn = (torch.rand(nu, generator=gen, device=dev) * 0.8 * Mb).round().long()
+            wild = torch.rand(nu, generator=gen, device=dev) < 0.05
+            Mw = torch.randint(1, 256, (nu,), generator=gen, device=dev)
+            Nw = (torch.rand(nu, generator=gen, device=dev) * (torch.clamp(257 - Mw, max=255) + 1)).floor().long()
+            Mb, Nn = torch.where(wild, Mw, Mb), torch.where(wild, Nw, Nn)
+            Nn = torch.minimum(Nn, 257 - Mb)
+        else:
+            L = all_MbN().to(dev)
+            idx = (torch.arange(nu, device=dev) + mbn[1]) % len(L)
+            Mb, Nn = L[idx, 0], L[idx, 1]
+        s.Mb, s.Nn = Mb, Nn
+        s.d4 = (Mb | (Nn << 8)).to(torch.int32)
+        s.var = torch.randint(0, 256, (S * C,), generator=gen, dtype=torch.int64, device=dev).to(torch.uint8) if var else None
+        if nm is None:
+            s.flags = s.fl = None
+        else:
+            cg = torch.Generator().manual_seed(int(torch.randint(0, 2**31 - 1, (1,), generator=gen, device=dev)))
+            s.flags, s.fl = (t.to(dev) for t in make_flags(S, C, nm, cg))
+
+    def to(s, dev):
+        for k in ("base", "p4", "d4", "flags", "fl", "Mb", "Nn", "var"):
+            v = getattr(s, k)
+            if v is not None:
+                setattr(s, k, v.to(dev))
+        return s
+
+    def nbytes(s, level):
+        b = s.base.numel() * 4 + (0 if s.var is None else s.var.numel())
+        if level >= 4:
+            b += s.z["p4"] + s.d4.numel() * 4 + (0 if s.flags is None else s.flags.numel() * 8)
+        return b
+
+
+def had_dn(ex):
+    """width of the down projection's input rotation (128 unless the expert says 512)"""
+    return int(getattr(ex, "had_dn", 128) or 128)
+
+
+class Expert:
+    """Seeded synthetic expert: gate|up planes (2I x H), down planes (H x I) and the scale vector
+    `signs` = fp16 [H su_g | I sv_g | I sv_u | I su_d | H sv_o | H su_u].  Input scales are +-1 (Hadamard signs);
+    output scales are +-1 (sv=None, the reference's synthetic default) or |N(0, sv)|."""
+
+    def __init__(s, H, I, seed, nm_gu=None, nm_dn=None, dev="cuda", rk_gu=0, rk_dn=0, mbn="rand", var=False, sv=None,
+                 gen_device="cpu"):
+        gen = torch.Generator(device=gen_device).manual_seed(seed)
+        s.gu = Proj(2 * I, H, gen, nm_gu, rk_gu, mbn, var).to(dev)
+        mbn_dn = mbn if mbn == "rand" else ("exh", mbn[1] + (2 * I // 16) * (H // 128))
+        s.dn = Proj(H, I, gen, nm_dn, rk_dn, mbn_dn, var).to(dev)
+        sg = (torch.randint(0, 2, (3 * H + 3 * I,), generator=gen, device=gen_device) * 2 - 1).float()
+        if sv is not None:
+            mag = (torch.randn(3 * H + 3 * I, generator=gen, device=gen_device) * sv).abs()
+            out = torch.zeros(3 * H + 3 * I, dtype=torch.bool, device=gen_device)
+            out[H:H + 2 * I] = True
+            out[H + 3 * I:2 * H + 3 * I] = True
+            sg = torch.where(out, mag, sg)
+        s.signs = sg.half().to(dev)
+        s.H, s.I, s.lr, s.lr4, s.rg, s.rd = H, I, None, None, 0, 0
+
+    def set_lr(s, Vg, U2g, U2u, U4g, U4u, Vd, U2d, U4d):
+        """low-rank plane (fp16): Vg [rg,H], U*g/U*u [rg,I], Vd [rd,I], U*d [rd,H]"""
+        cat = lambda *t: torch.cat([x.reshape(-1) for x in t]).half().contiguous()
+        s.rg, s.rd = Vg.shape[0], Vd.shape[0]
+        if s.rg + s.rd == 0:
+            s.lr = s.lr4 = None
+            return s
+        s.lr = cat(Vg, U2g, U2u, Vd, U2d).to(s.signs.device)
+        s.lr4 = cat(U4g, U4u, U4d).to(s.signs.device)
+        return s
+
+    def bytes(s, level):
+        """packed plane bytes a kernel reads for this expert at `level` (scales not included)"""
+        return s.gu.nbytes(level) + s.dn.nbytes(level)
+
+
+def base_code(p):
+    return int(getattr(p, "bk", 0) or 0)
+
+
+def entry(ex, level):
+    """device table row (int64 [20]) of an expert at a level"""
+    e = torch.zeros(TBL_W, dtype=torch.int64)
+    e[0] = level
+    for off, p in ((1, ex.gu), (5, ex.dn)):
+        for i, k in enumerate(("base", "p4", "d4", "flags")):
+            t = getattr(p, k)
+            e[off + i] = 0 if t is None else t.data_ptr()
+    e[9] = ex.signs.data_ptr()
+    e[10], e[11] = ex.gu.rk, ex.dn.rk
+    for i, p in ((12, ex.gu), (13, ex.dn)):
+        v = getattr(p, "var", None)
+        e[i] = 0 if v is None else v.data_ptr()
+    if getattr(ex, "lr", None) is not None:
+        e[14], e[15], e[16], e[17] = ex.lr.data_ptr(), ex.lr4.data_ptr(), ex.rg, ex.rd
+    w = had_dn(ex)
+    e[18] = 0 if w == 128 else w
+    e[19] = base_code(ex.gu) | base_code(ex.dn) << 8
+    return e
+
+
+class MoELayer:
+    """Device table [E, 20] plus the workspaces of the decode path for up to Bmax tokens (Bmax <= 32).
+
+    Rows are flipped in place (`set`, or a Mailbox), which keeps a captured CUDA graph valid."""
+
+    def __init__(s, E, H, I, nm_gu=0, nm_dn=0, Bmax=4, topk=8, G=4, dev="cuda", mod=None):
+        s.M = mod or _ext
+        s.E, s.H, s.I, s.nm_gu, s.nm_dn, s.G, s.Bmax, s.topk = E, H, I, nm_gu, nm_dn, G, Bmax, topk
+        s.table = torch.zeros(E, TBL_W, dtype=torch.int64, device=dev)
+        s.out = torch.zeros(Bmax, H, dtype=torch.float32, device=dev)
+        s.hits_ptr = 0      # set to a (host-mapped) int32 [E] pointer to export routing hits
+
+    def set(s, e, ex, level):
+        w = had_dn(ex)
+        assert w in (128, 512) and s.I % w == 0, f"in_had_down {w} must be 128 or 512 and divide I={s.I}"
+        if getattr(ex, "lr", None) is not None:
+            assert ex.rg <= 4 and ex.rd <= 4 and ex.lr.dtype == torch.float16
+        bks = (base_code(ex.gu), base_code(ex.dn))
+        if bks != (0, 0):
+            bkm = s.M.bk_codes()
+            assert bkm[0] >> bks[0] & 1 and bkm[1] >> bks[1] & 1, f"base K code gu {bks[0]} / dn {bks[1]} not compiled (bk_codes {bkm})"
+        if level == 4:
+            rkm = s.M.rk_codes()
+            assert rkm[0] >> ex.gu.rk & 1 and rkm[1] >> ex.dn.rk & 1, f"residual K code gu {ex.gu.rk} / dn {ex.dn.rk} not compiled (rk_codes {rkm})"
+        s.table[e].copy_(entry(ex, level).to(s.table.device), non_blocking=False)
+
+
+class Mailbox:
+    """Graph-safe table updates: call .apply() inside the captured graph before the layer; stage rows from a side stream."""
+
+    def __init__(s, layer):
+        E, dev = layer.E, layer.table.device
+        s.L = layer
+        s.stage = torch.zeros(E, TBL_W, dtype=torch.int64, device=dev)
+        s.seq = torch.zeros(E, dtype=torch.int32, device=dev)
+        s.applied = torch.zeros(E, dtype=torch.int32, device=dev)
+        s.applied_host = torch.zeros(E, dtype=torch.int32).pin_memory()
+        s.hseq = [0] * E
+        s.pins = []
+
+    def apply(s):
+        s.L.M.mailbox(s.L.table, s.stage, s.seq, s.applied, s.applied_host.data_ptr())
+
+    def post(s, e, row, stream):
+        """enqueue on `stream` (after any plane copy already enqueued there): stage[e] = row; seq[e] += 1"""
+        assert s.done(e), "one outstanding op per expert"
+        s.hseq[e] += 1
+        r = row.pin_memory()
+        q = torch.tensor([s.hseq[e]], dtype=torch.int32).pin_memory()
+        s.pins += [r, q]
+        with torch.cuda.stream(stream):
+            s.stage[e].copy_(r, non_blocking=True)
+            s.seq[e:e + 1].copy_(q, non_blocking=True)
+
+    def done(s, e):
+        return int(s.applied_host[e]) == s.hseq[e]
