@@ -1,0 +1,323 @@
+#!/usr/bin/env python
+"""Benchmark of the NestQuant MoE layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): the GLM-5-shaped layer of the reference's decode benchmark - 256 routed experts, top-8, hidden 6144,
+expert intermediate 2048, the 77 most-routed experts at level 4 (gate|up residual K 2, down K 2.3125), the rest at
+level 2, Zipf(1.1)-biased routing tuned so that ~63 % of the picks hit level-4 experts - and ONE token per step.
+A step is one layer call (routing + rotation, gate|up GEMV + SwiGLU, down GEMV + combine).  All data is synthetic
+and seeded (nestquant_b200/synth.py).
+
+The line printed by rank 0:
+  value      packed plane bytes + scales of the activated experts / device time, GB/s, summed over the timed steps
+             (inputs resident in HBM; L2 flushed between steps by writing a 256 MB buffer)
+  e2e        the same metric through the public API with host buffers: pinned x -> device, layer, out -> host
+  roofline   the gate|up GEMV kernel (dominant): algorithmic bytes per launch / its own CUDA-event time, against the
+             measured HBM copy bandwidth of this pool
+  cpu_baseline   the CPU oracle port (oracle/nq_oracle.c, all host threads) on one full step of the same workload
+
+With N > 1 (torchrun, one rank per GPU) the experts are split contiguously across the ranks (expert-parallel): every
+rank runs the token through its resident experts and the partial outputs are summed with an NCCL all-reduce inside
+the timed region; value = bytes read by all ranks / max-over-ranks time (strong scaling: the work of one token is fixed).
+
+--impl reference times the reference's CPU algorithm (the oracle port; the reference itself is Python/torch and
+cannot travel to the GPU box) on a bounded sample of the same workload: per step the first two picks of the token.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "moe_decode_1tok_hbm_gbs"
+UNIT = "GB/s"
+N_LEVEL4 = 77
+SEED = 20240
+# DRAM bytes / algorithmic bytes of the gate|up GEMV kernel from the ncu capture summarised in
+# profiles/gemv_gate_up_glm_1tok.md (101.56 MB read + 3.20 MB written for 100.97 MB of planes and scales)
+NCU_TRAFFIC_RATIO = 1.037
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """samples SM clocks and throttle reasons (NVML, read-only) every few milliseconds while the timed region runs"""
+
+    def __init__(self, index):
+        self.index, self.rows, self.stop = index, [], threading.Event()
+        self.thread = threading.Thread(target=self.run, daemon=True)
+        self.max_mhz = None
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+            while not self.stop.is_set():
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.rows.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), [n for n, bit in names.items() if r & bit]))
+                self.stop.wait(0.005)
+        except Exception:
+            self.run_smi()
+
+    def run_smi(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self.stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                c = [v.strip() for v in out.split(",")]
+                self.max_mhz = int(c[1])
+                self.rows.append((int(c[0]), [n for n, v in zip(names, c[2:]) if v.lower().startswith("active")]))
+            except Exception:
+                pass
+            self.stop.wait(0.2)
+
+    def __enter__(self):
+        self.thread.start(); time.sleep(0.05); return self
+
+    def __exit__(self, *a):
+        self.stop.set(); self.thread.join(timeout=6)
+
+    def summary(self):
+        sm = sorted(r[0] for r in self.rows)
+        reasons = sorted({n for r in self.rows for n in r[1]})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(self.rows)}
+
+
+def workload(world, rank):
+    import torch
+    from nestquant_b200 import synth
+    cfg = synth.GLM
+    E, topk = cfg["E"], cfg["topk"]
+    bias = synth.zipf_bias(E, SEED)
+    levels = synth.level_map(E, bias, N_LEVEL4)
+    beta = synth.fit_beta(levels, bias, E, topk, 0.63)
+    per = E // world
+    owned = list(range(rank * per, (rank + 1) * per))
+    local = [lv if e in set(owned) else 0 for e, lv in enumerate(levels)]
+    return cfg, bias, beta, levels, local, owned
+
+
+def oracle_step(experts_np, levels, x, sel, rw, picks=None):
+    """the CPU oracle on one token: decode the picked experts and run the layer; returns (seconds, bytes)"""
+    from oracle import nq_oracle as O
+    for ex in experts_np.values():
+        ex._cache.clear()
+    if picks is not None:
+        sel, rw = sel[:, :picks], rw[:, :picks]
+    t = time.perf_counter()
+    O.moe_ref(experts_np, levels, x, sel, rw, keep_cache=False)
+    return time.perf_counter() - t
+
+
+def run_reference(args):
+    """CPU arm: the oracle port of the reference's torch path, all host threads, on a bounded sample per step."""
+    import numpy as np
+    import torch
+    from nestquant_b200 import moe, synth
+    from oracle import nq_oracle as O
+    from tests.util import expert_to_oracle
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cfg, bias, beta, levels, _, _ = workload(1, 0)
+    E, topk, H, I = cfg["E"], cfg["topk"], cfg["H"], cfg["I"]
+    picks = 2
+    times, nbytes = [], []
+    for step in range(args.warmup + args.steps):
+        sel, rw = synth.routing(1, E, topk, SEED + 1 + step, bias, beta)
+        x = synth.tokens(1, H, SEED + 7 + step)
+        exs = {}
+        for e in sel[0, :picks].tolist():
+            ex = moe.Expert(H, I, seed=SEED * 100003 + e, dev="cpu", rk_gu=0, rk_dn=7, var=True, sv=0.02)
+            exs[e] = expert_to_oracle(ex)
+        b = sum(moe_bytes(H, I, levels[e]) for e in exs)
+        dt = oracle_step(exs, levels, x.numpy(), sel.numpy(), rw.numpy(), picks)
+        if step >= args.warmup:
+            times.append(dt); nbytes.append(b)
+    val = sum(nbytes) / sum(times) / 1e9
+    cores = O.lib().nqo_threads()
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "glm5_moe_layer_decode_1tok", "experts": E, "topk": topk, "hidden": H, "intermediate": I,
+                       "level4_experts": N_LEVEL4, "sample": f"first {picks} of the token's {topk} picks per step"},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"first {picks} picks of one token per step (decode + fp32 matmuls), {args.steps} steps"},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def moe_bytes(H, I, level):
+    """packed plane bytes + scales of one expert at a level (gate|up code 0, down code 7, ring signs on)"""
+    from nestquant_b200 import moe
+    b = 0
+    for N, K, rk in ((2 * I, H, 0), (H, I, 7)):
+        z = moe.proj_sizes(N, K, None, rk)
+        b += z["base"] + z["S"] * z["C"]
+        if level >= 4:
+            b += z["p4"] + z["d4"]
+    return b + (3 * H + 3 * I) * 2
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from nestquant_b200 import build as nqbuild, synth
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the hot path has no CPU fallback)")
+    world, rank, local_rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run); WORLD_SIZE is {world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    nqbuild.build()
+
+    cfg, bias, beta, levels, local, owned = workload(world, rank)
+    E, topk, H, I = cfg["E"], cfg["topk"], cfg["H"], cfg["I"]
+    L, experts = synth.build_layer(cfg, local, seed=SEED, dev=dev, Bmax=4, owned=owned)
+    total = args.warmup + args.steps
+    sels, rws, xs, nbytes, nbytes_gu = [], [], [], [], []
+    for step in range(total):
+        sel, rw = synth.routing(1, E, topk, SEED + 1 + step, bias, beta)
+        sels.append(sel.to(dev)); rws.append(rw.to(dev)); xs.append(synth.tokens(1, H, SEED + 7 + step))
+        act = [e for e in set(sel.reshape(-1).tolist()) if local[e] > 0]
+        nbytes.append(sum(experts[e].bytes(local[e]) + (3 * H + 3 * I) * 2 for e in act))
+        nbytes_gu.append(sum(experts[e].gu.nbytes(local[e]) + (2 * H + 2 * I) * 2 for e in act))
+    xd = [x.to(dev) for x in xs]
+    xh = [x.pin_memory() for x in xs]
+    out_h = torch.empty(1, H, dtype=torch.float32).pin_memory()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def layer(i, x):
+        out = L(x, sels[i], rws[i])
+        if world > 1:
+            dist.all_reduce(out)
+        return out
+
+    # ---- device-resident timing: one event pair per step, L2 flushed (untimed) between steps
+    for i in range(args.warmup):
+        flush.zero_(); layer(i, xd[i])
+    barrier()
+    pairs = []
+    with ClockSampler(local_rank) as clk:
+        t_wall = time.perf_counter()
+        for i in range(args.warmup, total):
+            flush.zero_()
+            a, b = ev(), ev()
+            a.record(); layer(i, xd[i]); b.record()
+            pairs.append((a, b))
+        barrier()
+        t_wall = time.perf_counter() - t_wall
+    us = torch.tensor([a.elapsed_time(b) * 1e3 for a, b in pairs], dtype=torch.float64, device=dev)
+    by = torch.tensor(nbytes[args.warmup:], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(us, op=dist.ReduceOp.MAX); dist.all_reduce(by, op=dist.ReduceOp.SUM)
+    us_total, by_total = float(us.sum()), float(by.sum())
+
+    # ---- dominant kernel alone (gate|up GEMV): event pairs around which = 1 calls (route + gate|up), minus the route kernel
+    k_us, r_us = [], []
+    for i in range(args.warmup, total):
+        flush.zero_()
+        a, b, c = ev(), ev(), ev()
+        a.record(); L(xd[i], sels[i], rws[i], which=0); b.record(); L(xd[i], sels[i], rws[i], which=1); c.record()
+        k_us.append((a, b, c))
+    torch.cuda.synchronize()
+    gu_us = sum(max(b.elapsed_time(c) - a.elapsed_time(b), 0.0) * 1e3 for a, b, c in k_us)
+    gu_bytes = float(sum(nbytes_gu[args.warmup:]))
+
+    # ---- end to end through the public API with host buffers
+    for i in range(args.warmup):
+        L(xh[i].to(dev, non_blocking=True), sels[i], rws[i])
+    barrier()
+    e2e_us = []
+    for i in range(args.warmup, total):
+        flush.zero_(); torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = layer(i, xh[i].to(dev, non_blocking=True))
+        out_h.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+        e2e_us.append((time.perf_counter() - t0) * 1e6)
+    e2 = torch.tensor(e2e_us, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2, op=dist.ReduceOp.MAX)
+    e2e_total = float(e2.sum())
+
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        value = by_total / us_total / 1e3
+        achieved = gu_bytes / gu_us / 1e3
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": us_total / args.steps / 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f16", "data": "synthetic",
+                "config": {"workload": "glm5_moe_layer_decode_1tok", "experts": E, "topk": topk, "hidden": H, "intermediate": I,
+                           "level4_experts": N_LEVEL4, "level4_pick_share": round(synth.share_at_level4(levels, bias, beta, E, topk), 3),
+                           "tokens_per_step": 1, "parallelism": f"ep{world}", "l2": "flushed between steps (256 MB write)"},
+                "layer_us": us_total / args.steps, "bytes_per_step": by_total / args.steps,
+                "e2e": {"value": by_total / e2e_total / 1e3, "unit": UNIT, "h2d_bytes_per_step": H * 2,
+                        "d2h_bytes_per_step": H * 4, "layer_us": e2e_total / args.steps},
+                "gpu_launches": 3 * args.steps,
+                "roofline": {"kernel": "gemv_kernel<0> (gate|up GEMV + SwiGLU)", "bound": "hbm", "achieved": achieved, "peak": peak,
+                             "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind + " copy bandwidth",
+                             "frac_of_nominal_8000": achieved / 8000.0, "us_per_launch": gu_us / args.steps,
+                             "bytes_per_launch": gu_bytes / args.steps,
+                             "traffic": NCU_TRAFFIC_RATIO * gu_bytes / args.steps},
+                "clocks": clk.summary()}
+        # CPU baseline: the oracle port on one full step (rank 0, N = 1 only)
+        if world == 1:
+            from oracle import nq_oracle as O
+            from tests.util import expert_to_oracle
+            i = args.warmup
+            act = sorted(set(sels[i].reshape(-1).tolist()))
+            exs = {e: expert_to_oracle(experts[e]) for e in act}
+            ref_us = oracle_step(exs, levels, xs[i].numpy(), sels[i].cpu().numpy(), rws[i].cpu().numpy()) * 1e6
+            line["cpu_baseline"] = {"value": nbytes[i] / ref_us / 1e3, "unit": UNIT, "cores": O.lib().nqo_threads(), "kind": "port",
+                                    "sample": "one full 1-token step (8 experts: dense decode + fp32 matmuls)", "layer_us": ref_us}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -63,6 +63,53 @@ int nq_pf_decode(const int64_t* table, const int32_t* experts, int n_experts, vo
 int nq_mailbox(int64_t* table, const int64_t* stage, const int32_t* seq, int32_t* applied, int32_t* applied_host,
                int E, void* stream);
 
+/* ---- decode path: one MoE layer call for 1..NQ_MAX_TOKENS tokens -------------------------------------------
+ * Replaces moe_forward() (sm120/nqmoe.cu:858-907).  The argument block carries the same tensors, in the same roles,
+ * as the reference's positional arguments; element counts travel with the pointers because nothing here can ask a
+ * tensor for its size.  Differences a caller can see:
+ *   - up to 32 tokens per call (the reference: 8), B * topk <= 256;
+ *   - split-k partial sums are written to acc_gu / acc_d and summed in a fixed order: results are bitwise repeatable,
+ *     and those two buffers need no zeroing.  cnt_gu, cnt_d and wq must be zero on entry and are zero again on exit;
+ *   - workspace sizes depend on the k-splits: ask nq_moe_workspace() (the reference sized them from B * topk alone);
+ *     h also holds the rotated inputs and cnt_h holds the run list;
+ *   - if no resident expert with a non-zero weight is picked at all, out is written with zeros
+ *     (the reference leaves it untouched, sm120/nqmoe.cu:789);
+ *   - tiling is two integers (ks_gu, ks_dn = k-slices per strip) instead of cfg_gu / cfg_dn = (cpw, sb, nst[, pers]).
+ * Three launches on `stream`; every routing, level and pointer decision is read on the device, so the call can be
+ * captured in a CUDA graph and replayed while a mailbox flips table rows. */
+typedef struct NqMoeWorkspace {
+    size_t acc_gu_floats, h_halves, acc_d_floats, cnt_gu_ints, cnt_d_ints, wq_ints, zd_floats, cnt_h_ints;
+} NqMoeWorkspace;
+
+/* Required element counts of the workspace tensors for a call shape. */
+int nq_moe_workspace(int B, int topk, int H, int I, int ks_gu, int ks_dn, NqMoeWorkspace* out);
+
+typedef struct NqMoeForward {
+    const void* x;            /* fp16 [B][H] */
+    const int64_t* sel;       /* int64 [B][topk] expert ids */
+    const void* rw;           /* fp16 [B][topk] routing weights */
+    const int64_t* table;     /* int64 [E][20] */
+    float* out;               /* fp32 [>= B][H], overwritten */
+    float* acc_gu;            /* workspaces, see nq_moe_workspace */
+    void* h;
+    float* acc_d;
+    int32_t* cnt_gu;
+    int32_t* cnt_d;
+    int32_t* wq;
+    float* zd;
+    int32_t* cnt_h;
+    int32_t* hits;            /* optional int32 [E] pick counters (device or host-mapped), or NULL */
+    size_t out_floats, acc_gu_floats, h_halves, acc_d_floats, cnt_gu_ints, cnt_d_ints, wq_ints, zd_floats, cnt_h_ints;
+    int B, topk, E, H, I;
+    int nm_gu, nm_dn;         /* flagged chunks per strip of masked experts (per layer) */
+    int ks_gu, ks_dn;         /* k-slices per strip: must divide H/128 and I/128 */
+    int G;                    /* ring width, must be 4 */
+    int force_level;          /* 0, or 2 / 4 to override the level of every resident expert */
+    int which;                /* bit 0: gate|up, bit 1: down + combine */
+} NqMoeForward;
+
+int nq_moe_forward(const NqMoeForward* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,7 +40,8 @@ def _newest_dep():
 
 def _compile(src, verbose):
     obj = os.path.join(OBJ, src[:-3] + ".o")
-    cmd = [nvcc()] + ARCH + FLAGS + ["-c", os.path.join(CSRC, src), "-o", obj]
+    defs = ["-D" + d for d in os.environ.get("NQ_DEFS", "").split(",") if d]     # e.g. NQ_DEFS=NQ_GEMV_DEPTH=4
+    cmd = [nvcc()] + ARCH + FLAGS + defs + ["-c", os.path.join(CSRC, src), "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     with open(obj[:-2] + ".ptxas.log", "w") as f:       # registers / spills / shared memory per kernel
         f.write(r.stderr)

@@ -16,6 +16,22 @@ MAX_PICKS = 256
 
 _p, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
 
+
+
+class NqMoeWorkspace(C.Structure):
+    _fields_ = [(n, _sz) for n in ("acc_gu_floats", "h_halves", "acc_d_floats", "cnt_gu_ints", "cnt_d_ints", "wq_ints",
+                                   "zd_floats", "cnt_h_ints")]
+
+
+class NqMoeForward(C.Structure):
+    _fields_ = ([(n, _p) for n in ("x", "sel", "rw", "table", "out", "acc_gu", "h", "acc_d", "cnt_gu", "cnt_d", "wq", "zd",
+                                   "cnt_h", "hits")] +
+                [(n, _sz) for n in ("out_floats", "acc_gu_floats", "h_halves", "acc_d_floats", "cnt_gu_ints", "cnt_d_ints",
+                                    "wq_ints", "zd_floats", "cnt_h_ints")] +
+                [(n, _i) for n in ("B", "topk", "E", "H", "I", "nm_gu", "nm_dn", "ks_gu", "ks_dn", "G", "force_level",
+                                   "which")])
+
+
 # name -> (restype, argtypes); mirrors include/nestquant_b200.h one to one
 SIGNATURES = {
     "nq_last_error": (C.c_char_p, []),
@@ -25,6 +41,8 @@ SIGNATURES = {
     "nq_plane_bytes": (_sz, [_sz, _i]),
     "nq_pf_decode": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
     "nq_mailbox": (_i, [_p, _p, _p, _p, _p, _i, _p]),
+    "nq_moe_workspace": (_i, [_i, _i, _i, _i, _i, _i, C.POINTER(NqMoeWorkspace)]),
+    "nq_moe_forward": (_i, [C.POINTER(NqMoeForward), _p]),
 }
 
 _lib = None

@@ -48,3 +48,46 @@ def pf_decode(table, experts, Wgu, Wdn, H, I, nm_gu, nm_dn, force_level=0):
                 raise NestQuantError(f"pf_decode sizes: {name} has {t.numel()} elements, needs {n}")
     check(lib().nq_pf_decode(ptr(table), ptr(experts), G, ptr(Wgu), ptr(Wdn), H, I, nm_gu, nm_dn, force_level,
                              current_stream()), "pf_decode")
+
+
+def default_ksplit(B, H, I):
+    """k-slices per strip (gate|up, down) for a B-token call: few tokens need more slices to fill 148 SMs"""
+    def pick(chunks, want):
+        for k in (want, 6, 4, 3, 2, 1):
+            if k <= want and chunks % k == 0:
+                return k
+        return 1
+    want_gu, want_dn = (4, 2) if B <= 2 else (2, 1) if B <= 8 else (1, 1)
+    return pick(H // 128, want_gu), pick(I // 128, want_dn)
+
+
+def moe_workspace(B, topk, H, I, ks_gu, ks_dn):
+    """element counts of the workspace tensors of moe_forward for a call shape"""
+    w = capi.NqMoeWorkspace()
+    check(lib().nq_moe_workspace(B, topk, H, I, ks_gu, ks_dn, C.byref(w)), "moe_workspace")
+    return {n: int(getattr(w, n)) for n, _ in capi.NqMoeWorkspace._fields_}
+
+
+def moe_forward(x, sel, rw, table, out, acc_gu, h, acc_d, cnt_gu, cnt_d, wq, I, nm_gu, nm_dn, cfg_gu, cfg_dn, G,
+                force_level, which, hits_ptr, zd, cnt_h):
+    """One MoE layer call on the decode path, positional arguments as in the reference's moe_forward.
+    cfg_gu / cfg_dn: [k-slices per strip] (entries after the first are accepted and ignored)."""
+    _need(x, torch.float16, "x"); _need(rw, torch.float16, "rw"); _need(sel, torch.int64, "sel")
+    _need(table, torch.int64, "table"); _need(out, torch.float32, "out"); _need(acc_gu, torch.float32, "acc_gu")
+    _need(h, torch.float16, "h"); _need(acc_d, torch.float32, "acc_d"); _need(zd, torch.float32, "zd")
+    for t, n in ((cnt_gu, "cnt_gu"), (cnt_d, "cnt_d"), (wq, "wq"), (cnt_h, "cnt_h")):
+        _need(t, torch.int32, n)
+    if x.dim() != 2 or sel.dim() != 2 or sel.shape[0] != x.shape[0] or rw.shape != sel.shape:
+        raise NestQuantError("moe_forward: x [B,H], sel [B,topk], rw [B,topk]")
+    a = capi.NqMoeForward()
+    for n, t in (("x", x), ("sel", sel), ("rw", rw), ("table", table), ("out", out), ("acc_gu", acc_gu), ("h", h),
+                 ("acc_d", acc_d), ("cnt_gu", cnt_gu), ("cnt_d", cnt_d), ("wq", wq), ("zd", zd), ("cnt_h", cnt_h)):
+        setattr(a, n, t.data_ptr())
+    a.hits = hits_ptr or None
+    a.out_floats, a.acc_gu_floats, a.h_halves, a.acc_d_floats = out.numel(), acc_gu.numel(), h.numel(), acc_d.numel()
+    a.cnt_gu_ints, a.cnt_d_ints, a.wq_ints, a.zd_floats, a.cnt_h_ints = (cnt_gu.numel(), cnt_d.numel(), wq.numel(),
+                                                                        zd.numel(), cnt_h.numel())
+    a.B, a.topk, a.E, a.H, a.I = x.shape[0], sel.shape[1], table.shape[0], x.shape[1], I
+    a.nm_gu, a.nm_dn, a.ks_gu, a.ks_dn = nm_gu, nm_dn, int(cfg_gu[0]), int(cfg_dn[0])
+    a.G, a.force_level, a.which = G, force_level, which
+    check(lib().nq_moe_forward(C.byref(a), current_stream()), "moe_forward")

@@ -256,12 +256,29 @@ class MoELayer:
 
     Rows are flipped in place (`set`, or a Mailbox), which keeps a captured CUDA graph valid."""
 
-    def __init__(s, E, H, I, nm_gu=0, nm_dn=0, Bmax=4, topk=8, G=4, dev="cuda", mod=None):
+    def __init__(s, E, H, I, nm_gu=0, nm_dn=0, Bmax=4, topk=8, G=4, dev="cuda", mod=None, ksplit=None):
+        """ksplit: optional (gate|up, down) k-slices per strip to size the workspaces for, when calls will override
+        the per-token-count default through cfg_gu / cfg_dn."""
         s.M = mod or _ext
         s.E, s.H, s.I, s.nm_gu, s.nm_dn, s.G, s.Bmax, s.topk = E, H, I, nm_gu, nm_dn, G, Bmax, topk
         s.table = torch.zeros(E, TBL_W, dtype=torch.int64, device=dev)
         s.out = torch.zeros(Bmax, H, dtype=torch.float32, device=dev)
         s.hits_ptr = 0      # set to a (host-mapped) int32 [E] pointer to export routing hits
+        s.cfg_gu = s.cfg_dn = None     # [k-slices per strip]; None = chosen from the token count of each call
+        # workspaces sized for the deepest k-split any call shape can ask for
+        ws = [s.M.moe_workspace(b, topk, H, I, *s.M.default_ksplit(b, H, I)) for b in range(1, Bmax + 1)]
+        if ksplit is not None:
+            ws.append(s.M.moe_workspace(Bmax, topk, H, I, *ksplit))
+        n = {k: max(w[k] for w in ws) for k in ws[0]}
+        f32, f16, i32 = torch.float32, torch.float16, torch.int32
+        s.acc_gu = torch.zeros(n["acc_gu_floats"], dtype=f32, device=dev)
+        s.h = torch.zeros(n["h_halves"], dtype=f16, device=dev)
+        s.acc_d = torch.zeros(n["acc_d_floats"], dtype=f32, device=dev)
+        s.cnt_gu = torch.zeros(n["cnt_gu_ints"], dtype=i32, device=dev)
+        s.cnt_d = torch.zeros(n["cnt_d_ints"], dtype=i32, device=dev)
+        s.wq = torch.zeros(n["wq_ints"], dtype=i32, device=dev)
+        s.zd = torch.zeros(n["zd_floats"], dtype=f32, device=dev)
+        s.cnt_h = torch.zeros(n["cnt_h_ints"], dtype=i32, device=dev)
 
     def set(s, e, ex, level):
         w = had_dn(ex)
@@ -276,6 +293,20 @@ class MoELayer:
             rkm = s.M.rk_codes()
             assert rkm[0] >> ex.gu.rk & 1 and rkm[1] >> ex.dn.rk & 1, f"residual K code gu {ex.gu.rk} / dn {ex.dn.rk} not compiled (rk_codes {rkm})"
         s.table[e].copy_(entry(ex, level).to(s.table.device), non_blocking=False)
+
+
+    def __call__(s, x, sel, rw, out=None, force_level=0, which=3, cfg_gu=None, cfg_dn=None, table=None):
+        """x fp16 [B,H], sel int64 [B,topk], rw fp16 [B,topk] -> fp32 [B,H] (s.out[:B] unless `out` is given).
+        table: optional [E,20] override of s.table.  Enqueued on the current stream; no host sync."""
+        assert x.dtype == torch.float16 and rw.dtype == torch.float16 and sel.dtype == torch.int64, (x.dtype, rw.dtype, sel.dtype)
+        B = x.shape[0]
+        assert B <= s.Bmax and sel.shape[1] == s.topk, f"layer was built for up to {s.Bmax} tokens, top-{s.topk}"
+        out = s.out[:B] if out is None else out
+        ks = s.M.default_ksplit(B, s.H, s.I)
+        s.M.moe_forward(x, sel, rw, s.table if table is None else table, out, s.acc_gu, s.h, s.acc_d, s.cnt_gu, s.cnt_d,
+                        s.wq, s.I, s.nm_gu, s.nm_dn, cfg_gu or s.cfg_gu or [ks[0]], cfg_dn or s.cfg_dn or [ks[1]], s.G,
+                        force_level, which, s.hits_ptr, s.zd, s.cnt_h)
+        return out
 
 
 class Mailbox:

@@ -1,0 +1,186 @@
+"""Decode-path layer (nq_moe_forward through MoELayer) against the reference-generated golden layer and the CPU oracle.
+Mirrors the reference's sm120/check.py (mixed levels 0/2/4 + mask mode, B = 1..4, routing patterns, repeatability,
+workspace clean on exit) and sm120/levelswitch_mbox.py (mailbox level switch)."""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nq_oracle as O
+from tests.golden_io import layer_from
+from tests.util import MAX_ABS_TOL, REL_L2_TOL, expert_to_device, expert_to_oracle, layer_errors
+
+pytestmark = pytest.mark.gpu
+
+
+def _routing(B, E, topk, gen, mode="rand", live=None):
+    live = list(range(E)) if live is None else live
+    rows = []
+    for b in range(B):
+        if mode == "same" and rows:
+            rows.append(rows[0])
+        else:
+            rows.append(gen.sample(live, topk))
+    sel = torch.tensor(rows, dtype=torch.long)
+    g = torch.Generator().manual_seed(gen.randrange(1 << 30))
+    w = torch.rand(sel.shape, generator=g) + 0.1
+    return sel, (w / w.sum(1, keepdim=True)).half()
+
+
+def _check(L, exs_o, levels, x, sel, rw, tag):
+    ref = O.moe_ref(exs_o, levels, x.cpu().numpy(), sel.numpy(), rw.numpy())
+    y = L(x.cuda(), sel.cuda(), rw.cuda()).clone()
+    y2 = L(x.cuda(), sel.cuda(), rw.cuda()).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2), f"{tag}: not bitwise repeatable"
+    ma, rl = layer_errors(y.cpu().numpy(), ref)
+    assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL, (tag, ma, rl)
+    assert rl <= 5e-4, (tag, rl)              # what the fp16-operand / fp32-accumulate path actually achieves
+    for t in (L.cnt_gu, L.cnt_d, L.wq):
+        assert int(t.abs().sum()) == 0, f"{tag}: counters not clean on exit"
+    return ma, rl
+
+
+def test_golden_layer():
+    from nestquant_b200 import moe
+    g = layer_from("layer.npz")
+    L = moe.MoELayer(g["E"], g["H"], g["I"], nm_gu=1, nm_dn=1, Bmax=8, topk=g["topk"])
+    keep = []
+    for e, eo in enumerate(g["experts"]):
+        if eo is None:
+            continue
+        ex = expert_to_device(eo); keep.append(ex)
+        L.set(e, ex, g["levels"][e])
+    x = torch.from_numpy(g["x"].copy()).cuda()
+    y = L(x, torch.from_numpy(g["sel"]).cuda(), torch.from_numpy(g["rw"].copy()).cuda())
+    torch.cuda.synchronize()
+    ma, rl = layer_errors(y.cpu().numpy(), g["out"])
+    assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL and rl <= 5e-4, (ma, rl)
+    assert not y[4].any()                    # token routed only to a level-0 expert
+
+
+@pytest.mark.parametrize("H,I", [(1024, 512), (768, 384)])
+def test_mixed_levels_vs_oracle(H, I):
+    """12 experts, levels 2/4/0, three masked (50 % of chunks refined), production window codes and signs"""
+    from nestquant_b200 import moe
+    NE, topk = 12, 4
+    nmg, nmd = H // 128 // 2, I // 128 // 2
+    masked = {1, 4, 8}
+    levels = [2, 4, 4, 2, 4, 4, 2, 4, 4, 4, 2, 0]
+    exs = [moe.Expert(H, I, seed=100 + i, nm_gu=nmg if i in masked else None, nm_dn=nmd if i in masked else None,
+                      rk_gu=(0, 6, 3)[i % 3], rk_dn=(7, 8, 0)[i % 3], var=i % 4 != 3, sv=0.02) for i in range(NE)]
+    exs_o = [expert_to_oracle(e) for e in exs]
+    L = moe.MoELayer(NE, H, I, nmg, nmd, Bmax=32, topk=topk)
+    for e in range(NE):
+        L.set(e, exs[e], levels[e])
+    rng = random.Random(0)
+    gen = torch.Generator().manual_seed(1)
+    for B in (1, 2, 3, 4, 8, 17, 32):
+        for mode in ("rand", "same"):
+            sel, rw = _routing(B, NE, topk, rng, mode)
+            if B == 3:
+                rw[1, 2] = 0                  # a zero-weight pick is skipped
+            x = torch.randn(B, H, generator=gen).bfloat16().half()
+            _check(L, exs_o, levels, x, sel, rw, (H, I, B, mode))
+
+
+def test_glm_shape_one_and_four_tokens():
+    from nestquant_b200 import moe
+    H, I, NE, topk = 6144, 2048, 10, 8
+    levels = [4, 2, 4, 4, 2, 4, 2, 4, 4, 2]
+    exs = [moe.Expert(H, I, seed=200 + i, rk_gu=0, rk_dn=7, var=True, sv=0.02) for i in range(NE)]
+    exs_o = [expert_to_oracle(e) for e in exs]
+    L = moe.MoELayer(NE, H, I, Bmax=4, topk=topk)
+    for e in range(NE):
+        L.set(e, exs[e], levels[e])
+    rng = random.Random(5)
+    gen = torch.Generator().manual_seed(2)
+    for B in (1, 4):
+        sel, rw = _routing(B, NE, topk, rng)
+        x = torch.randn(B, H, generator=gen).bfloat16().half()
+        _check(L, exs_o, levels, x, sel, rw, ("glm", B))
+        for e in exs_o:
+            e._cache.clear()
+
+
+def test_nothing_resident_gives_zeros_and_hits_are_counted():
+    from nestquant_b200 import moe
+    H, I, NE, topk = 256, 128, 4, 2
+    exs = [moe.Expert(H, I, seed=i, sv=0.02) for i in range(NE)]
+    L = moe.MoELayer(NE, H, I, Bmax=4, topk=topk)
+    for e in range(NE):
+        L.set(e, exs[e], 0 if e < 2 else 2)
+    hits = torch.zeros(NE, dtype=torch.int32, device="cuda")
+    L.hits_ptr = hits.data_ptr()
+    L.out.fill_(7.0)
+    x = torch.randn(2, H).half().cuda()
+    sel = torch.tensor([[0, 1], [1, 0]]).cuda()
+    rw = torch.tensor([[0.5, 0.5], [0.25, 0.0]]).half().cuda()
+    y = L(x, sel, rw)
+    torch.cuda.synchronize()
+    assert not y.any()
+    assert hits.tolist() == [1, 2, 0, 0]       # every pick with a non-zero weight, whatever its level
+    sel2 = torch.tensor([[0, 2], [3, 1]]).cuda()
+    y = L(x, sel2, rw)
+    torch.cuda.synchronize()
+    assert y[0].any() and y[1].any() and hits.tolist() == [2, 2, 1, 1]
+
+
+def test_bad_arguments_raise():
+    from nestquant_b200 import moe
+    from nestquant_b200.capi import NestQuantError
+    L = moe.MoELayer(4, 256, 128, Bmax=2, topk=2)
+    x = torch.zeros(2, 256, dtype=torch.float16, device="cuda")
+    sel = torch.zeros(2, 2, dtype=torch.long, device="cuda")
+    rw = torch.zeros(2, 2, dtype=torch.float16, device="cuda")
+    with pytest.raises(NestQuantError):
+        L(x, sel, rw, cfg_gu=[5])              # 2 chunks cannot be cut into 5 slices
+    with pytest.raises(NestQuantError):
+        L.M.moe_forward(x, sel, rw, L.table, L.out, L.acc_gu[:8], L.h, L.acc_d, L.cnt_gu, L.cnt_d, L.wq, 128, 0, 0, [1], [1],
+                        4, 0, 3, 0, L.zd, L.cnt_h)
+    with pytest.raises(NestQuantError):
+        L.M.moe_forward(x, sel, rw, L.table, L.out, L.acc_gu, L.h, L.acc_d, L.cnt_gu, L.cnt_d, L.wq, 128, 0, 0, [1], [1],
+                        2, 0, 3, 0, L.zd, L.cnt_h)   # ring width 2 is not built
+    with pytest.raises(AssertionError):
+        L(x.float(), sel, rw)
+
+
+def test_mailbox_switches_levels_inside_a_graph():
+    """Graph = [mailbox.apply, layer].  Rows staged on a side stream take effect at the next replay, never earlier."""
+    from nestquant_b200 import moe
+    H, I, NE, topk, B = 512, 256, 6, 3, 2
+    exs = [moe.Expert(H, I, seed=300 + i, rk_dn=7, var=True, sv=0.02) for i in range(NE)]
+    exs_o = [expert_to_oracle(e) for e in exs]
+    L = moe.MoELayer(NE, H, I, Bmax=B, topk=topk)
+    MB = moe.Mailbox(L)
+    levels = [2] * NE
+    for e in range(NE):
+        L.set(e, exs[e], 2)
+    rng = random.Random(9)
+    sel, rw = _routing(B, NE, topk, rng)
+    x = torch.randn(B, H).bfloat16().half()
+    xd, seld, rwd = x.cuda(), sel.cuda(), rw.cuda()
+    s = torch.cuda.Stream(); side = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            MB.apply(); L(xd, seld, rwd)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        MB.apply(); L(xd, seld, rwd)
+    torch.cuda.synchronize()
+    for step in range(6):
+        e = int(sel[0, step % topk])
+        new = 4 if levels[e] == 2 else 2
+        MB.post(e, moe.entry(exs[e], new), side)
+        side.synchronize()
+        g.replay(); torch.cuda.synchronize()
+        assert MB.done(e)
+        levels[e] = new
+        ref = O.moe_ref(exs_o, levels, x.numpy(), sel.numpy(), rw.numpy())
+        ma, rl = layer_errors(L.out[:B].cpu().numpy(), ref)
+        assert rl <= 5e-4, (step, rl)
+        stale = list(levels); stale[e] = 6 - new
+        _, rl_stale = layer_errors(L.out[:B].cpu().numpy(), O.moe_ref(exs_o, stale, x.numpy(), sel.numpy(), rw.numpy()))
+        assert rl_stale > 20 * rl              # the other level would be plainly wrong
