@@ -63,6 +63,35 @@ int nq_pf_decode(const int64_t* table, const int32_t* experts, int n_experts, vo
 int nq_mailbox(int64_t* table, const int64_t* stage, const int32_t* seq, int32_t* applied, int32_t* applied_host,
                int E, void* stream);
 
+/* ---- prefill path: stream-ordered helpers around the grouped GEMMs ---------------------------------------------
+ * Pairs = (token, expert) picks sorted by expert: pt[p] = token, pe[p] = expert, prw[p] = routing weight (fp16).
+ * R = number of pairs in this call.  z arrays are fp32 [R][4] (low-rank inputs, rank <= 4). */
+
+/* xg[p] = fp16(WHT128(x[pt[p]] * su_g)), xu[p] likewise with su_u, both [R][H]; zg[p][r] = x . V_gu[r].
+ * Pairs of level-0 experts are skipped (their rows are left untouched).
+ * Replaces pf_pre() (sm120/nqmoe.cu:1081-1117,1258-1267). */
+int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const int64_t* table, void* xg, void* xu, float* zg,
+              int H, int I, void* stream);
+
+/* acc_g, acc_u fp32 [R][I] (GEMM outputs) -> h fp16 [R][I] = WHT_w(silu(g) u su_d), g = WHT128(acc_g) sv_g + low rank,
+ * w = 128 or the expert's 512-wide rotation; zd[p][r] = (silu(g) u) . V_dn[r].
+ * Replaces pf_mid() (sm120/nqmoe.cu:1118-1203,1268-1277). */
+int nq_pf_mid(const float* acc_g, const float* acc_u, const float* zg, const int32_t* pe, int R, const int64_t* table, void* h,
+              float* zd, int H, int I, void* stream);
+
+/* out[pt[p]] += prw[p] * (WHT128(y[p]) * sv_o + low rank), y fp32 [R][H]; atomic adds into a caller-zeroed out.
+ * Replaces pf_post() (sm120/nqmoe.cu:1204-1240,1278-1287). */
+int nq_pf_post(const float* y, const float* zd, const int32_t* pt, const int32_t* pe, const void* prw, int R, const int64_t* table,
+               float* out, int H, int I, void* stream);
+
+/* Same sum without atomics: out[t] = sum over k in pick order of the pair at pos[t * topk + k]; out [T][H] is
+ * overwritten and bitwise repeatable.  No counterpart in the reference (its pf_post order depends on atomics). */
+int nq_pf_combine(const float* y, const float* zd, const int32_t* pos, const int64_t* sel, const void* rw, int T, int topk,
+                  const int64_t* table, int E, float* out, int H, int I, void* stream);
+
+/* hits[e] += counts[e] (hits may be host-mapped; NULL = no-op).  Replaces pf_hits() (sm120/nqmoe.cu:1241-1245,1288-1293). */
+int nq_pf_hits(const int32_t* counts, int32_t* hits, int E, void* stream);
+
 /* ---- decode path: one MoE layer call for 1..NQ_MAX_TOKENS tokens -------------------------------------------
  * Replaces moe_forward() (sm120/nqmoe.cu:858-907).  The argument block carries the same tensors, in the same roles,
  * as the reference's positional arguments; element counts travel with the pointers because nothing here can ask a

@@ -41,6 +41,11 @@ SIGNATURES = {
     "nq_plane_bytes": (_sz, [_sz, _i]),
     "nq_pf_decode": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
     "nq_mailbox": (_i, [_p, _p, _p, _p, _p, _i, _p]),
+    "nq_pf_pre": (_i, [_p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _p]),
+    "nq_pf_mid": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _i, _i, _p]),
+    "nq_pf_post": (_i, [_p, _p, _p, _p, _p, _i, _p, _p, _i, _i, _p]),
+    "nq_pf_combine": (_i, [_p, _p, _p, _p, _p, _i, _i, _p, _i, _p, _i, _i, _p]),
+    "nq_pf_hits": (_i, [_p, _p, _i, _p]),
     "nq_moe_workspace": (_i, [_i, _i, _i, _i, _i, _i, C.POINTER(NqMoeWorkspace)]),
     "nq_moe_forward": (_i, [C.POINTER(NqMoeForward), _p]),
 }

@@ -50,6 +50,56 @@ def pf_decode(table, experts, Wgu, Wdn, H, I, nm_gu, nm_dn, force_level=0):
                              current_stream()), "pf_decode")
 
 
+def pf_pre(x, pt, pe, table, xg, xu, zg, I):
+    """per pair (sorted by expert): xg / xu = fp16(WHT128(x * su_g / su_u)) [R,H], zg = x V_gu^T [R,4]"""
+    _need(x, torch.float16, "x"); _need(pt, torch.int32, "pt"); _need(pe, torch.int32, "pe"); _need(table, torch.int64, "table")
+    _need(xg, torch.float16, "xg"); _need(xu, torch.float16, "xu"); _need(zg, torch.float32, "zg")
+    R, H = pt.numel(), x.shape[1]
+    if pe.numel() < R or xg.numel() < R * H or xu.numel() < R * H or zg.numel() < R * 4:
+        raise NestQuantError("pf_pre sizes")
+    check(lib().nq_pf_pre(ptr(x), ptr(pt), ptr(pe), R, ptr(table), ptr(xg), ptr(xu), ptr(zg), H, I, current_stream()), "pf_pre")
+
+
+def pf_mid(acc_g, acc_u, zg, pe, table, h, zd, H, I):
+    """acc_g / acc_u fp32 [R,I] -> h fp16 [R,I] (rotations, scales, SwiGLU), zd [R,4]"""
+    _need(acc_g, torch.float32, "acc_g"); _need(acc_u, torch.float32, "acc_u"); _need(zg, torch.float32, "zg")
+    _need(pe, torch.int32, "pe"); _need(table, torch.int64, "table"); _need(h, torch.float16, "h"); _need(zd, torch.float32, "zd")
+    R = pe.numel()
+    if acc_g.numel() < R * I or acc_u.numel() < R * I or h.numel() < R * I or zd.numel() < R * 4 or zg.numel() < R * 4:
+        raise NestQuantError("pf_mid sizes")
+    check(lib().nq_pf_mid(ptr(acc_g), ptr(acc_u), ptr(zg), ptr(pe), R, ptr(table), ptr(h), ptr(zd), H, I, current_stream()), "pf_mid")
+
+
+def pf_post(y, zd, pt, pe, prw, table, out, I):
+    """out[pt[p]] += prw[p] * (WHT128(y[p]) * sv_o + low rank); out fp32 [T,H], zeroed by the caller"""
+    _need(y, torch.float32, "y"); _need(zd, torch.float32, "zd"); _need(pt, torch.int32, "pt"); _need(pe, torch.int32, "pe")
+    _need(prw, torch.float16, "prw"); _need(table, torch.int64, "table"); _need(out, torch.float32, "out")
+    R, H = pt.numel(), out.shape[1]
+    if y.numel() < R * H or zd.numel() < R * 4 or prw.numel() < R or pe.numel() < R:
+        raise NestQuantError("pf_post sizes")
+    check(lib().nq_pf_post(ptr(y), ptr(zd), ptr(pt), ptr(pe), ptr(prw), R, ptr(table), ptr(out), H, I, current_stream()), "pf_post")
+
+
+def pf_combine(y, zd, pos, sel, rw, table, out, I):
+    """out[t] = sum_k rw[t,k] * (WHT128(y[pos[t,k]]) * sv_o + low rank) in pick order; out fp32 [T,H] is overwritten"""
+    _need(y, torch.float32, "y"); _need(zd, torch.float32, "zd"); _need(pos, torch.int32, "pos"); _need(sel, torch.int64, "sel")
+    _need(rw, torch.float16, "rw"); _need(table, torch.int64, "table"); _need(out, torch.float32, "out")
+    T, topk = sel.shape
+    H = out.shape[1]
+    if pos.numel() < T * topk or rw.numel() < T * topk or out.numel() < T * H or y.numel() < T * topk * H or zd.numel() < T * topk * 4:
+        raise NestQuantError("pf_combine sizes")
+    check(lib().nq_pf_combine(ptr(y), ptr(zd), ptr(pos), ptr(sel), ptr(rw), T, topk, ptr(table), table.shape[0], ptr(out), H, I,
+                              current_stream()), "pf_combine")
+
+
+def pf_hits(counts, hits_ptr):
+    """hits[e] += counts[e]; hits_ptr: raw (host-mapped) int32 [E] pointer or 0"""
+    if not hits_ptr:
+        return
+    _need(counts, torch.int32, "counts")
+    check(lib().nq_pf_hits(ptr(counts), hits_ptr, counts.numel(), current_stream()), "pf_hits")
+
+
 def default_ksplit(B, H, I):
     """k-slices per strip (gate|up, down) for a B-token call: few tokens need more slices to fill 148 SMs"""
     def pick(chunks, want):

@@ -1,0 +1,101 @@
+"""Prefill path (MoELayer.prefill and the pf_* helpers through the C ABI) against the reference-generated golden layers
+and the CPU oracle.  Mirrors the reference's sm120/smoke_prefill.py: prefill == decode-path slices == dense reference,
+hits exported, plus the low-rank plane and the 512-wide rotation (sm120/check_lr.py)."""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nq_oracle as O
+from tests.golden_io import layer_from
+from tests.util import MAX_ABS_TOL, REL_L2_TOL, expert_to_device, expert_to_oracle, layer_errors
+
+pytestmark = pytest.mark.gpu
+
+
+def _layer_from_golden(name, **kw):
+    from nestquant_b200 import moe
+    g = layer_from(name)
+    L = moe.MoELayer(g["E"], g["H"], g["I"], Bmax=8, topk=g["topk"], **kw)
+    keep = []
+    for e, eo in enumerate(g["experts"]):
+        if eo is not None:
+            ex = expert_to_device(eo); keep.append(ex)
+            L.set(e, ex, g["levels"][e])
+    x = torch.from_numpy(g["x"].copy()).cuda()
+    return g, L, keep, x, torch.from_numpy(g["sel"]).cuda(), torch.from_numpy(g["rw"].copy()).cuda()
+
+
+@pytest.mark.parametrize("deterministic", [True, False])
+def test_golden_layer_prefill(deterministic):
+    g, L, keep, x, sel, rw = _layer_from_golden("layer.npz", nm_gu=1, nm_dn=1)
+    y = L.prefill(x, sel, rw, deterministic=deterministic)
+    torch.cuda.synchronize()
+    ma, rl = layer_errors(y.cpu().numpy(), g["out"])
+    assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL and rl <= 5e-4, (ma, rl)
+    assert not y[4].any()
+    if deterministic:
+        assert torch.equal(y, L.prefill(x, sel, rw))
+
+
+def test_golden_layer_with_low_rank_and_wide_rotation():
+    g, L, keep, x, sel, rw = _layer_from_golden("layer_lr.npz")
+    y = L.prefill(x, sel, rw, R=4, G=1)           # tiny chunks: exercises the group / chunk loops
+    torch.cuda.synchronize()
+    ma, rl = layer_errors(y.cpu().numpy(), g["out"])
+    assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL and rl <= 5e-4, (ma, rl)
+    # without the low-rank plane the result must be plainly different (the plane is really applied)
+    for ex in keep:
+        ex.lr = ex.lr4 = None
+    for e, ex in enumerate(keep):
+        L.set(e, ex, g["levels"][e])
+    y0 = L.prefill(x, sel, rw)
+    torch.cuda.synchronize()
+    _, rl0 = layer_errors(y0.cpu().numpy(), g["out"])
+    assert rl0 > 20 * max(rl, 1e-6)
+
+
+def test_prefill_matches_decode_path_and_oracle():
+    from nestquant_b200 import moe
+    H, I, NE, topk, T = 1024, 512, 16, 4, 96
+    nmg, nmd = H // 128 // 2, I // 128 // 2
+    levels = [2, 4, 4, 0, 4, 2, 4, 4, 2, 4, 4, 2, 4, 0, 2, 4]
+    masked = {2, 9}
+    exs = [moe.Expert(H, I, seed=700 + i, nm_gu=nmg if i in masked else None, nm_dn=nmd if i in masked else None,
+                      rk_gu=(0, 6)[i % 2], rk_dn=7, var=True, sv=0.02) for i in range(NE)]
+    L = moe.MoELayer(NE, H, I, nmg, nmd, Bmax=32, topk=topk)
+    for e in range(NE):
+        L.set(e, exs[e], levels[e])
+    hits = torch.zeros(NE, dtype=torch.int32, device="cuda")
+    L.hits_ptr = hits.data_ptr()
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(T, H, generator=g).bfloat16().half()
+    logits = torch.randn(T, NE, generator=g) + torch.linspace(2, -2, NE)      # skewed: some experts get many tokens
+    tv, sel = logits.topk(topk, dim=1)
+    rw = torch.softmax(tv, 1).half()
+    rw[7, 1] = 0
+    xd, seld, rwd = x.cuda(), sel.cuda(), rw.cuda()
+    y = L.prefill(xd, seld, rwd, R=64, G=3)
+    torch.cuda.synchronize()
+    want_hits = torch.bincount(sel[rw != 0].reshape(-1), minlength=NE).tolist()
+    assert hits.tolist() == want_hits
+    ref = O.moe_ref([expert_to_oracle(e) for e in exs], levels, x.numpy(), sel.numpy(), rw.numpy())
+    ma, rl = layer_errors(y.cpu().numpy(), ref)
+    assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL and rl <= 5e-4, (ma, rl)
+    L.hits_ptr = 0
+    ys = torch.cat([L(xd[i:i + 32], seld[i:i + 32], rwd[i:i + 32]).clone() for i in range(0, T, 32)])
+    ma2, rl2 = layer_errors(y.cpu().numpy(), ys.cpu().numpy())
+    assert rl2 <= 5e-4, rl2                       # same math, different fp32 accumulation order
+
+
+def test_pf_helpers_reject_bad_sizes():
+    from nestquant_b200 import ext
+    from nestquant_b200.capi import NestQuantError
+    t = torch.zeros(4, 20, dtype=torch.int64, device="cuda")
+    x = torch.zeros(2, 256, dtype=torch.float16, device="cuda")
+    idx = torch.zeros(3, dtype=torch.int32, device="cuda")
+    with pytest.raises(NestQuantError):
+        ext.pf_pre(x, idx, idx, t, x, x, torch.zeros(3, 4, device="cuda"), 128)       # xg too small for 3 pairs
+    with pytest.raises(NestQuantError):
+        ext.pf_pre(x.float(), idx, idx, t, x, x, torch.zeros(3, 4, device="cuda"), 128)
