@@ -89,6 +89,21 @@ int nq_pf_post(const float* y, const float* zd, const int32_t* pt, const int32_t
 int nq_pf_combine(const float* y, const float* zd, const int32_t* pos, const int64_t* sel, const void* rw, int T, int topk,
                   const int64_t* table, int E, float* out, int H, int I, void* stream);
 
+/* Fused prefill GEMM (decode in shared memory -> tcgen05 / TMEM): the replacement of the reference's
+ * pf_decode + grouped GEMM pair (sm120/moe.py:303-324, sm120/pf_gemm.py:7-34, sm120/nqmoe.cu:1013-1080); the dense fp16
+ * weights are never materialised.
+ *   nq_pf_plan   from per-expert pair counts (int32 [E], pairs sorted by expert) build the pass list on the device:
+ *                a pass = one resident expert x up to 512 of its pairs.  plan: int32 [nq_pf_plan_ints(E, pairs)].
+ *   nq_pf_gemm   down = 0: acc_g[p] = xg[p] Wg^T, acc_u[p] = xu[p] Wu^T (act0 = xg, act1 = xu fp16 [pairs][H];
+ *                out0 = acc_g, out1 = acc_u fp32 [pairs][I]); down = 1: y[p] = h[p] Wd^T (act0 = h fp16 [pairs][I],
+ *                out0 = y fp32 [pairs][H], act1 / out1 unused).  Rows of pairs whose expert is not resident are not
+ *                written.  status: int32 [1] on the device, set to 1 if a device-side wait timed out (bounded waits;
+ *                the outputs are then invalid) - read it after synchronising. */
+int nq_pf_plan_ints(int E, int pairs);
+int nq_pf_plan(const int32_t* counts, const int64_t* table, int E, int pairs, int32_t* plan, int plan_ints, void* stream);
+int nq_pf_gemm(const int64_t* table, const int32_t* plan, const void* act0, const void* act1, int pairs, float* out0, float* out1,
+               int H, int I, int nm_gu, int nm_dn, int down, int32_t* status, void* stream);
+
 /* hits[e] += counts[e] (hits may be host-mapped; NULL = no-op).  Replaces pf_hits() (sm120/nqmoe.cu:1241-1245,1288-1293). */
 int nq_pf_hits(const int32_t* counts, int32_t* hits, int E, void* stream);
 

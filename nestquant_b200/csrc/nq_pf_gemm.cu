@@ -1,0 +1,484 @@
+// Prefill grouped GEMM with the trellis decode fused in: acc[pair][n] = sum_k act[pair][k] * W_expert(pair)[n][k].
+//
+// Replaces the reference's prefill sequence pf_decode -> dense fp16 weights in VRAM -> cuBLAS / Triton grouped GEMM
+// (sm120/moe.py:303-324, sm120/pf_gemm.py, sm120/nqmoe.cu:1013-1080): the dense weights are never written to HBM.
+//
+// One work item = (pass, 128-row weight group): a pass is one expert and up to 512 of its tokens.  Per item a CTA
+// walks K in blocks of 64:
+//   warp 0        TMA: the tokens' activation tile [ntok x 64] fp16 (SWIZZLE_128B boxes of 64 rows) -> shared memory
+//   warps 2..17   decode: warp (h, s) streams strip s of the group with cp.async, decodes k-steps 4h..4h+3 of each unit
+//                 in registers (bit-exact fp16) and stores them as the UMMA A tile [128 x 64] (K-major, no swizzle) of
+//                 k-block 2 c + h
+//   warp 1        one thread issues tcgen05.mma (M 128 = weight rows, N = tokens, K 16) into a [128 x 512] fp32
+//                 accumulator in TMEM; tcgen05.commit frees the stage
+//   warps 2..17   epilogue: tcgen05.ld the accumulator and store fp32 rows acc[pair][128 columns] (coalesced)
+// Each decoded weight is used for every token of the pass, so decode cost is paid once per expert (for up to 512
+// tokens).  Tensor-pipe bound by intent; the decode instruction rate is the practical limit.
+// Every mbarrier wait is bounded: on time-out the CTA raises status[0], drains and returns.
+#include <cuda.h>
+
+#include "nq_common.cuh"
+#include "nq_stream.cuh"
+#include "nq_unit.cuh"
+
+namespace nq {
+
+constexpr int kPfTokens = 512;                       // tokens per pass = TMEM columns
+constexpr int kPfBoxRows = 64;                       // token rows per TMA box
+constexpr int kPfABytes = 128 * 64 * 2;              // A tile of one k-block
+constexpr int kPfBBytes = kPfTokens * 64 * 2;        // token tile of one k-block
+constexpr int kPfRingDepth = 3;
+constexpr int kPfDecodeWarps = 16;
+constexpr int kPfThreads = 32 * (2 + kPfDecodeWarps);
+constexpr int kPfSmem = 2 * kPfBBytes + 2 * kPfABytes + kPfDecodeWarps * kPfRingDepth * kStageBytes + 1024 + 256;
+constexpr unsigned long long kPfWaitNs = 2000000000ull;   // a wait that lasts 2 s is treated as a hang
+
+struct PfPass { int expert, row0, ntok, pad; };
+
+struct PfGemmArgs
+{
+    const int64_t* table;
+    const int* plan;          // [0] number of passes, then PfPass records from int 4 on
+    float* out0; float* out1; // gate|up: acc_g, acc_u [pairs][I]; down: y [pairs][H]
+    int* status;              // [0] != 0: a wait timed out (device side), the results are invalid
+    int H, I, nm_gu, nm_dn, down;
+};
+
+// ---------------------------------------------------------------- mbarrier / tcgen05 / TMA primitives
+__device__ __forceinline__ uint32_t saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
+}
+// bounded wait for the phase with the given parity; false = aborted (by this or another thread of the CTA)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
+{
+    const uint32_t a = saddr(bar);
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i)
+    {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+        if ((i & 255u) == 255u)
+        {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > kPfWaitNs) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(saddr(dst)), "l"(map), "r"(saddr(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]; fp16 operands, fp32 accumulate
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// shared-memory operand descriptor: start address, leading / stride byte offsets (all >> 4), descriptor version 1,
+// layout 0 = no swizzle, 2 = 128-byte swizzle
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout)
+{
+    const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (((lbo >> 4) & 0x3FFFu) << 16);
+    const uint32_t hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (layout << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+// kind::f16 instruction descriptor: D fp32, A/B fp16 K-major, M 128, N tokens
+__device__ __forceinline__ uint32_t instr_desc(int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | (8u << 24); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, "
+                 "%26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                   "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                   "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                   "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- decode warps: one half (4 k-steps) of each unit of a strip
+// A tile layout (K-major, no swizzle): 8 x 16-byte core matrices, 128 B apart along K, 1024 B apart along rows, i.e.
+// byte (row, k) = (row / 8) * 1024 + (k / 8) * 128 + (row % 8) * 16 + (k % 8) * 2.  A lane's fragment register of
+// k-step t, rows g + 8 (q & 1), k = 16 t + 2 t4 + 8 (q >> 1) lands at strip * 2048 + lane * 4 + constant.
+template <int HALF>
+struct ATileSink
+{
+    uint8_t* dst;   // A tile + strip * 2048 + lane * 4
+    template <int T>
+    __device__ __forceinline__ void operator()(std::integral_constant<int, T>, const uint32_t (&a)[4]) const
+    {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) *(uint32_t*)(dst + (q & 1) * 1024 + (2 * T + (q >> 1)) * 128) = a[q];
+    }
+};
+
+// k-steps 4 HALF .. 4 HALF + 3 of a unit whose words are in registers
+template <bool RES, int RC, int HALF, class Sink>
+__device__ __forceinline__ void decode_half(uint32_t* wb, uint32_t* wr, const UnitConsts& k, int lane, Sink&& sink)
+{
+    const int nxt = ring_next_lane(lane);
+    extend_stream<128>(wb, __shfl_sync(0xffffffffu, wb[0], nxt));
+    if constexpr (RES) extend_stream<Pattern<RC>::kBits>(wr, __shfl_sync(0xffffffffu, wr[0], nxt));
+    static_for<4>([&](auto tc) {
+        constexpr int T = decltype(tc)::value, TT = 4 * HALF + T;
+        uint32_t a[4];
+        a[0] = decode_pair<RES, RC, 4 * TT + 0>(wb, wr, k);
+        a[1] = decode_pair<RES, RC, 4 * TT + 1>(wb, wr, k);
+        a[2] = decode_pair<RES, RC, 4 * TT + 2>(wb, wr, k);
+        a[3] = decode_pair<RES, RC, 4 * TT + 3>(wb, wr, k);
+        sink(tc, a);
+    });
+}
+
+struct PfShared
+{
+    uint64_t full_b[2], full_a[2], empty[2], acc_full, acc_empty;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+// one decode warp, one item: stream its strip over all chunks, fill the A tile of k-block 2 c + HALF for every chunk c.
+// `it` counts the k-blocks this warp has filled so far (phase of the stage barriers).  false = aborted.
+template <bool REFINED, int RC, int HALF>
+__device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int C, int NS, int nm, int lane, uint8_t* a_tile,
+                                             uint8_t* ring, PfShared* sh, uint32_t& it)
+{
+    unsigned long long fl = ~0ull;
+    if (REFINED && P.flags) fl = __ldg((const unsigned long long*)P.flags + strip);
+    const size_t res_nrec = (size_t)NS * (P.flags ? nm : C) * 32;
+    const size_t unit0 = (size_t)strip * C;
+    auto res_unit = [&](int ch) -> size_t {
+        return P.flags ? (size_t)strip * nm + __popcll(fl & ((1ull << ch) - 1ull)) : unit0 + ch;
+    };
+    uint32_t var_lo = 0, var_hi = 0, dl_lo = 0, dl_hi = 0;      // per-unit scalars, one chunk per lane
+    {
+        const int ca = lane, cb = 32 + lane;
+        if (P.var) { if (ca < C) var_lo = __ldg(P.var + unit0 + ca); if (cb < C) var_hi = __ldg(P.var + unit0 + cb); }
+        if constexpr (REFINED)
+        {
+            if (ca < C && ((fl >> ca) & 1ull)) dl_lo = __ldg(P.d4 + res_unit(ca));
+            if (cb < C && ((fl >> cb) & 1ull)) dl_hi = __ldg(P.d4 + res_unit(cb));
+        }
+    }
+    auto issue = [&](int ch, uint8_t* st) {
+        cp_async16(st + lane * 16, (const uint8_t*)(P.base + (unit0 + ch) * 32 + lane));
+        if constexpr (REFINED)
+            if ((fl >> ch) & 1ull) copy_record<RC>(st + 512, P.p4, res_unit(ch) * 32 + lane, res_nrec, lane);
+    };
+#pragma unroll
+    for (int d = 0; d < kPfRingDepth - 1; ++d)
+    {
+        if (d < C) issue(d, ring + d * kStageBytes);
+        cp_async_commit();
+    }
+    int slot = 0, slot_in = kPfRingDepth - 1;
+    bool ok = true;
+    for (int ch = 0; ch < C; ++ch)
+    {
+        if (ch + kPfRingDepth - 1 < C) issue(ch + kPfRingDepth - 1, ring + slot_in * kStageBytes);
+        cp_async_commit();
+        cp_async_wait<kPfRingDepth - 1>();
+        const uint8_t* st = ring + slot * kStageBytes;
+        slot = slot + 1 == kPfRingDepth ? 0 : slot + 1;
+        slot_in = slot_in + 1 == kPfRingDepth ? 0 : slot_in + 1;
+        const uint32_t vb = __shfl_sync(0xffffffffu, ch < 32 ? var_lo : var_hi, ch & 31);
+        const uint32_t sign2 = ((vb >> (lane >> 2)) & 1u) * 0x80008000u;
+        const uint4 b = *(const uint4*)(st + lane * 16);
+        uint32_t wb[6] = {b.x, b.y, b.z, b.w, 0u, 0u};
+        // the MMAs that read this stage two k-blocks ago must have completed (stage HALF is only ever filled by this half)
+        if (ok && !mbar_wait(&sh->empty[HALF], ((it >> 1) & 1u) ^ 1u, &sh->abort_flag)) ok = false;
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        const ATileSink<HALF> sink{a_tile + strip % 8 * 2048 + lane * 4};
+        bool refined = false;
+        if constexpr (REFINED) refined = (fl >> ch) & 1ull;
+        if (ok)
+        {
+            if (refined)
+            {
+                const uint32_t dl = __shfl_sync(0xffffffffu, ch < 32 ? dl_lo : dl_hi, ch & 31);
+                uint32_t wr[Pattern<RC>::kWords + 2];
+                read_record<RC>(wr, st + 512, res_unit(ch) * 32 + lane, lane);
+                decode_half<true, RC, HALF>(wb, wr, consts_level4(dl, sign2), lane, sink);
+            }
+            else
+                decode_half<false, 0, HALF>(wb, nullptr, consts_level2(sign2), lane, sink);
+            fence_async_smem();                      // generic-proxy stores -> visible to the tensor core (async proxy)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->full_a[HALF]);
+        }
+        it += 2;
+    }
+    cp_async_wait<0>();
+    return ok;
+}
+
+template <int HALF>
+__device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int rc, int strip, int C, int NS, int nm, int lane,
+                                            uint8_t* a_tile, uint8_t* ring, PfShared* sh, uint32_t& it)
+{
+#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV, HALF>(P, strip, C, NS, nm, lane, a_tile, ring, sh, it)
+    if (level < 4) NQ_RUN(false, 0);
+    switch (rc)
+    {
+        case 1: NQ_RUN(true, 1);
+        case 2: NQ_RUN(true, 2);
+        case 3: NQ_RUN(true, 3);
+        case 4: NQ_RUN(true, 4);
+        case 5: NQ_RUN(true, 5);
+        case 6: NQ_RUN(true, 6);
+        case 7: NQ_RUN(true, 7);
+        case 8: NQ_RUN(true, 8);
+        case 9: NQ_RUN(true, 9);
+        default: NQ_RUN(true, 0);
+    }
+#undef NQ_RUN
+}
+
+// grid = resident CTAs (one per SM), 576 threads
+__global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_constant__ CUtensorMap tmap0,
+                                                                const __grid_constant__ CUtensorMap tmap1, PfGemmArgs a)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* b_tiles = smem;                                  // 2 x [512 tokens][64 k] fp16, 128-byte swizzle (TMA)
+    uint8_t* a_tiles = smem + 2 * kPfBBytes;                  // 2 x [128 rows][64 k] fp16, core-matrix layout
+    uint8_t* rings = a_tiles + 2 * kPfABytes;                 // per decode warp: kPfRingDepth plane stages
+    PfShared* sh = (PfShared*)(rings + kPfDecodeWarps * kPfRingDepth * kStageBytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0)
+    {
+        for (int s = 0; s < 2; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->full_a[s], kPfDecodeWarps / 2); mbar_init(&sh->empty[s], 1); }
+        mbar_init(&sh->acc_full, 1); mbar_init(&sh->acc_empty, kPfDecodeWarps);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1)
+    {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&sh->tmem_base)), "r"(kPfTokens) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+
+    const int N = a.down ? a.H : 2 * a.I, K = a.down ? a.I : a.H, C = K / 128, NS = N / 16, groups = N / 128, nkb = K / 64;
+    const int npass = a.plan[0], nitems = npass * groups;
+    const PfPass* passes = (const PfPass*)(a.plan + 4);
+    uint32_t it = 0, nitem = 0;     // k-blocks / items handled so far by this role (barrier phases)
+
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x, ++nitem)
+    {
+        const int pi = item / groups, wg = item - pi * groups;
+        const PfPass ps = passes[pi];
+        const int ntok16 = (ps.ntok + 15) & ~15, nbox = (ps.ntok + kPfBoxRows - 1) / kPfBoxRows;
+        const int up = !a.down && wg >= a.I / 128;
+        if (warp == 0)
+        {
+            // ---- token tiles by TMA
+            if (lane == 0)
+            {
+                const CUtensorMap* map = up ? &tmap1 : &tmap0;
+                for (int kb = 0; kb < nkb; ++kb, ++it)
+                {
+                    const int s = it & 1;
+                    if (!mbar_wait(&sh->empty[s], ((it >> 1) & 1u) ^ 1u, &sh->abort_flag)) break;
+                    mbar_expect_tx(&sh->full_b[s], (uint32_t)nbox * kPfBoxRows * 128);
+                    for (int j = 0; j < nbox; ++j)
+                        tma_load_2d(b_tiles + s * kPfBBytes + j * kPfBoxRows * 128, map, kb * 64, ps.row0 + j * kPfBoxRows, &sh->full_b[s]);
+                }
+            }
+        }
+        else if (warp == 1)
+        {
+            // ---- MMA issue
+            if (lane == 0)
+            {
+                bool ok = mbar_wait(&sh->acc_empty, (nitem & 1u) ^ 1u, &sh->abort_flag);   // epilogue of the previous item has drained TMEM
+                tc_fence_after();
+                for (int kb = 0; ok && kb < nkb; ++kb, ++it)
+                {
+                    const int s = it & 1;
+                    const uint32_t ph = (it >> 1) & 1u;
+                    if (!mbar_wait(&sh->full_b[s], ph, &sh->abort_flag) || !mbar_wait(&sh->full_a[s], ph, &sh->abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t abase = saddr(a_tiles + s * kPfABytes), bbase = saddr(b_tiles + s * kPfBBytes);
+                    for (int sub = 0; sub * 256 < ntok16; ++sub)
+                    {
+                        const int n = ntok16 - sub * 256 < 256 ? ntok16 - sub * 256 : 256;
+                        const uint32_t idesc = instr_desc(n);
+#pragma unroll
+                        for (int k16 = 0; k16 < 4; ++k16)
+                            tc_mma_f16(tmem + sub * 256, smem_desc(abase + k16 * 256, 128, 1024, 0),
+                                       smem_desc(bbase + sub * 256 * 128 + k16 * 32, 16, 1024, 2), idesc, (kb | k16) != 0);
+                    }
+                    tc_commit(&sh->empty[s]);          // arrives when the MMAs above have read the stage
+                }
+                if (ok) tc_commit(&sh->acc_full);
+            }
+        }
+        else
+        {
+            // ---- decode, then epilogue
+            const int dw = warp - 2, half = dw >> 3, sidx = dw & 7;
+            const int64_t* row = a.table + (int64_t)ps.expert * kTableWidth;
+            const int level = (int)row[0];
+            const ProjPlanes P = planes_from_row(row, a.down);
+            const int rc = (int)row[10 + a.down], nm = a.down ? a.nm_dn : a.nm_gu;
+            uint8_t* ring = rings + dw * kPfRingDepth * kStageBytes;
+            uint32_t my_it = it + half;                 // this warp fills k-blocks 2 c + half
+            bool ok = half ? decode_item<1>(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, a_tiles + kPfABytes, ring, sh, my_it)
+                           : decode_item<0>(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, a_tiles, ring, sh, my_it);
+            it += nkb;
+            if (ok && lane == 0 && !mbar_wait(&sh->acc_full, nitem & 1u, &sh->abort_flag)) ok = false;
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            if (ok)
+            {
+                tc_fence_after();
+                // TMEM lanes 32 q .. 32 q + 31 (the quarter this warp may read) = weight rows; 128 token columns per warp
+                const int q = warp & 3, cpart = dw >> 2;
+                const int ncol = (up ? wg - a.I / 128 : wg) * 128 + q * 32 + lane;
+                float* out = up ? a.out1 : a.out0;
+                const int ld = a.down ? a.H : a.I;
+                for (int c0 = cpart * 128; c0 < cpart * 128 + 128 && c0 < ntok16; c0 += 32)
+                {
+                    uint32_t v[32];
+                    tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c0, v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c0 + j < ps.ntok) out[(size_t)(ps.row0 + c0 + j) * ld + ncol] = __uint_as_float(v[j]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->acc_empty);
+            }
+        }
+        if (sh->abort_flag) break;
+    }
+    if (sh->abort_flag && threadIdx.x == 0) atomicExch(a.status, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPfTokens) : "memory");
+}
+
+// ---------------------------------------------------------------- pass plan (device side, no host sync)
+// counts[e] = routed pairs of expert e (pairs are sorted by expert).  A pass = one expert x up to 512 of its pairs;
+// experts at level 0 get none.  plan: [0] passes, [1] pairs covered, then PfPass records from int 4 on.
+__global__ void pf_plan_kernel(const int* __restrict__ counts, const int64_t* __restrict__ table, int E, int* plan, int max_passes)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    PfPass* out = (PfPass*)(plan + 4);
+    int n = 0, row = 0, covered = 0;
+    for (int e = 0; e < E; ++e)
+    {
+        const int c = counts[e];
+        if (c > 0 && table[(int64_t)e * kTableWidth] > 0)
+            for (int t0 = 0; t0 < c && n < max_passes; t0 += kPfTokens)
+            {
+                out[n].expert = e; out[n].row0 = row + t0; out[n].ntok = c - t0 < kPfTokens ? c - t0 : kPfTokens; out[n].pad = 0;
+                covered += out[n].ntok; ++n;
+            }
+        row += c;
+    }
+    plan[0] = n; plan[1] = covered; plan[2] = plan[3] = 0;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// tensor map of a row-major fp16 matrix [rows][cols]: boxes of 64 columns x 64 rows, 128-byte swizzle, zero fill
+static int make_tile_map(CUtensorMap* map, const void* base, size_t rows, size_t cols)
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn)
+    {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p)
+            return fail(NQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        fn = (EncodeTiledFn)p;
+    }
+    const cuuint64_t dims[2] = {cols, rows}, strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)kPfBoxRows}, estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return NQ_OK;
+}
+
+}  // namespace nq
+
+extern "C" {
+
+int nq_pf_plan_ints(int E, int pairs) { return 4 + 4 * (E + pairs / nq::kPfTokens + 1); }
+
+int nq_pf_plan(const int32_t* counts, const int64_t* table, int E, int pairs, int32_t* plan, int plan_ints, void* stream)
+{
+    NQ_REQUIRE(counts && table && plan && E > 0 && pairs >= 0, "nq_pf_plan: bad arguments");
+    NQ_REQUIRE(plan_ints >= nq_pf_plan_ints(E, pairs), "nq_pf_plan: plan needs %d ints", nq_pf_plan_ints(E, pairs));
+    nq::pf_plan_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counts, table, E, plan, (plan_ints - 4) / 4);
+    return nq::check_launch("nq_pf_plan");
+}
+
+int nq_pf_gemm(const int64_t* table, const int32_t* plan, const void* act0, const void* act1, int pairs, float* out0, float* out1,
+               int H, int I, int nm_gu, int nm_dn, int down, int32_t* status, void* stream)
+{
+    NQ_REQUIRE(table && plan && act0 && out0 && status, "nq_pf_gemm: null pointer");
+    NQ_REQUIRE(down || (act1 && out1), "nq_pf_gemm: the gate|up projection needs both activation matrices and both outputs");
+    NQ_REQUIRE(H > 0 && I > 0 && H % 128 == 0 && I % 128 == 0 && H / 128 <= 64 && I / 128 <= 64, "nq_pf_gemm: H = %d, I = %d", H, I);
+    NQ_REQUIRE(pairs >= 0, "nq_pf_gemm: pairs = %d", pairs);
+    if (pairs == 0) return NQ_OK;
+    NQ_REQUIRE(nq::aligned16(act0) && nq::aligned16(act1) && nq::aligned16(out0), "nq_pf_gemm: matrices must be 16-byte aligned");
+    static int ctas = 0;
+    if (!ctas)
+    {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaFuncSetAttribute((const void*)nq::pf_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, nq::kPfSmem) != cudaSuccess)
+            return nq::fail(NQ_ERR_CUDA, "nq_pf_gemm: cannot reserve %d bytes of shared memory", nq::kPfSmem);
+        ctas = sms;
+    }
+    CUtensorMap m0, m1;
+    const size_t K = down ? I : H;
+    if (int e = nq::make_tile_map(&m0, act0, (size_t)pairs, K)) return e;
+    if (int e = nq::make_tile_map(&m1, down ? act0 : act1, (size_t)pairs, K)) return e;
+    nq::PfGemmArgs a{};
+    a.table = table; a.plan = plan; a.out0 = out0; a.out1 = out1; a.status = status;
+    a.H = H; a.I = I; a.nm_gu = nm_gu; a.nm_dn = nm_dn; a.down = down ? 1 : 0;
+    nq::pf_gemm_kernel<<<ctas, nq::kPfThreads, nq::kPfSmem, (cudaStream_t)stream>>>(m0, m1, a);
+    return nq::check_launch("nq_pf_gemm");
+}
+
+}  // extern "C"

@@ -92,6 +92,31 @@ def pf_combine(y, zd, pos, sel, rw, table, out, I):
                               current_stream()), "pf_combine")
 
 
+def pf_plan_ints(E, pairs):
+    return int(lib().nq_pf_plan_ints(E, pairs))
+
+
+def pf_plan(counts, table, plan, pairs):
+    """pass list of the fused prefill GEMM from per-expert pair counts (int32 [E], device); plan int32 [pf_plan_ints]"""
+    _need(counts, torch.int32, "counts"); _need(table, torch.int64, "table"); _need(plan, torch.int32, "plan")
+    check(lib().nq_pf_plan(ptr(counts), ptr(table), table.shape[0], pairs, ptr(plan), plan.numel(), current_stream()), "pf_plan")
+
+
+def pf_gemm(table, plan, act0, act1, out0, out1, H, I, nm_gu, nm_dn, down, status):
+    """fused decode + grouped GEMM of one projection over the expert-sorted pairs (see nq_pf_gemm)"""
+    _need(table, torch.int64, "table"); _need(plan, torch.int32, "plan"); _need(act0, torch.float16, "act0")
+    _need(out0, torch.float32, "out0"); _need(status, torch.int32, "status")
+    pairs, K, N = act0.shape[0], (I if down else H), (H if down else I)
+    if act0.dim() != 2 or act0.shape[1] != K or out0.numel() < pairs * N:
+        raise NestQuantError("pf_gemm sizes")
+    if not down:
+        _need(act1, torch.float16, "act1"); _need(out1, torch.float32, "out1")
+        if act1.shape != act0.shape or out1.numel() < pairs * N:
+            raise NestQuantError("pf_gemm sizes")
+    check(lib().nq_pf_gemm(ptr(table), ptr(plan), ptr(act0), ptr(act1), pairs, ptr(out0), ptr(out1), H, I, nm_gu, nm_dn,
+                           1 if down else 0, ptr(status), current_stream()), "pf_gemm")
+
+
 def pf_hits(counts, hits_ptr):
     """hits[e] += counts[e]; hits_ptr: raw (host-mapped) int32 [E] pointer or 0"""
     if not hits_ptr:

@@ -12,6 +12,7 @@ import math
 
 import torch
 
+from . import capi
 from . import ext as _ext
 
 TBL_W = 20
@@ -309,11 +310,14 @@ class MoELayer:
         return out
 
 
-    def prefill(s, x, sel, rw, out=None, R=None, G=None, table=None, deterministic=True):
+    def prefill(s, x, sel, rw, out=None, R=None, G=None, table=None, deterministic=True, fused=True):
         """T > Bmax tokens: every routed expert decoded once (level read from the live table row), grouped GEMMs with fp32
         outputs, same math as __call__.  x fp16 [T,H], sel int64 [T,topk], rw fp16 [T,topk] -> fp32 [T,H].
         R: pairs per scratch chunk, G: experts decoded per group.  deterministic: sum each token's picks in pick order
-        (needs an fp32 [T*topk, H] buffer) instead of atomic adds.  One host sync (expert counts); not graph-capturable."""
+        (needs an fp32 [T*topk, H] buffer) instead of atomic adds.
+        fused=True: the trellis decode runs inside the grouped GEMM (tcgen05 / TMEM), dense weights never touch HBM and the
+        pass list is built on the device; the only host sync is the status read at the end.  fused=False: the reference's
+        structure (decode G experts to dense fp16, per-expert library GEMMs, one host sync for the counts)."""
         assert x.dtype == torch.float16 and rw.dtype == torch.float16 and sel.dtype == torch.int64, (x.dtype, rw.dtype, sel.dtype)
         T, k = sel.shape
         H, I, E, M, dev = s.H, s.I, s.E, s.M, x.device
@@ -329,6 +333,28 @@ class MoELayer:
         cnt = torch.zeros(E, dtype=i32, device=dev).scatter_add_(0, flat, one)
         if s.hits_ptr:
             M.pf_hits(torch.zeros(E + 1, dtype=i32, device=dev).scatter_add_(0, torch.where(rwf != 0, flat, E), one)[:E].contiguous(), s.hits_ptr)
+        if fused:
+            P = T * k
+            pos = torch.empty(P, dtype=i32, device=dev)
+            pos[order] = torch.arange(P, dtype=i32, device=dev)
+            plan = torch.empty(M.pf_plan_ints(E, P), dtype=i32, device=dev)
+            M.pf_plan(cnt, tb, plan, P)
+            status = torch.zeros(1, dtype=i32, device=dev)
+            xg, xu = torch.empty(P, H, dtype=f16, device=dev), torch.empty(P, H, dtype=f16, device=dev)
+            zg, zd = torch.zeros(P, 4, dtype=f32, device=dev), torch.zeros(P, 4, dtype=f32, device=dev)
+            M.pf_pre(x, pt, pe, tb, xg, xu, zg, I)
+            acc_g, acc_u = torch.empty(P, I, dtype=f32, device=dev), torch.empty(P, I, dtype=f32, device=dev)
+            M.pf_gemm(tb, plan, xg, xu, acc_g, acc_u, H, I, s.nm_gu, s.nm_dn, False, status)
+            del xg, xu
+            hbuf = torch.empty(P, I, dtype=f16, device=dev)
+            M.pf_mid(acc_g, acc_u, zg, pe, tb, hbuf, zd, H, I)
+            del acc_g, acc_u
+            y = torch.empty(P, H, dtype=f32, device=dev)
+            M.pf_gemm(tb, plan, hbuf, None, y, None, H, I, s.nm_gu, s.nm_dn, True, status)
+            M.pf_combine(y, zd, pos, sel, rw, tb, out, I)
+            if int(status.item()):
+                raise capi.NestQuantError("prefill: a device-side wait timed out inside the grouped GEMM; results are invalid")
+            return out
         cnt = cnt.cpu().tolist()
         start, o = [0] * E, 0
         for e in range(E):

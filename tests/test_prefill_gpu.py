@@ -27,24 +27,25 @@ def _layer_from_golden(name, **kw):
     return g, L, keep, x, torch.from_numpy(g["sel"]).cuda(), torch.from_numpy(g["rw"].copy()).cuda()
 
 
-@pytest.mark.parametrize("deterministic", [True, False])
-def test_golden_layer_prefill(deterministic):
+@pytest.mark.parametrize("deterministic,fused", [(True, True), (True, False), (False, False)])
+def test_golden_layer_prefill(deterministic, fused):
     g, L, keep, x, sel, rw = _layer_from_golden("layer.npz", nm_gu=1, nm_dn=1)
-    y = L.prefill(x, sel, rw, deterministic=deterministic)
+    y = L.prefill(x, sel, rw, deterministic=deterministic, fused=fused)
     torch.cuda.synchronize()
     ma, rl = layer_errors(y.cpu().numpy(), g["out"])
     assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL and rl <= 5e-4, (ma, rl)
     assert not y[4].any()
     if deterministic:
-        assert torch.equal(y, L.prefill(x, sel, rw))
+        assert torch.equal(y, L.prefill(x, sel, rw, fused=fused))
 
 
 def test_golden_layer_with_low_rank_and_wide_rotation():
     g, L, keep, x, sel, rw = _layer_from_golden("layer_lr.npz")
-    y = L.prefill(x, sel, rw, R=4, G=1)           # tiny chunks: exercises the group / chunk loops
-    torch.cuda.synchronize()
-    ma, rl = layer_errors(y.cpu().numpy(), g["out"])
-    assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL and rl <= 5e-4, (ma, rl)
+    for fused in (True, False):
+        y = L.prefill(x, sel, rw, R=4, G=1, fused=fused)           # tiny chunks: exercises the group / chunk loops
+        torch.cuda.synchronize()
+        ma, rl = layer_errors(y.cpu().numpy(), g["out"])
+        assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL and rl <= 5e-4, (fused, ma, rl)
     # without the low-rank plane the result must be plainly different (the plane is really applied)
     for ex in keep:
         ex.lr = ex.lr4 = None
@@ -76,8 +77,11 @@ def test_prefill_matches_decode_path_and_oracle():
     rw = torch.softmax(tv, 1).half()
     rw[7, 1] = 0
     xd, seld, rwd = x.cuda(), sel.cuda(), rw.cuda()
-    y = L.prefill(xd, seld, rwd, R=64, G=3)
+    y_lib = L.prefill(xd, seld, rwd, R=64, G=3, fused=False)
+    hits.zero_()
+    y = L.prefill(xd, seld, rwd)
     torch.cuda.synchronize()
+    assert layer_errors(y.cpu().numpy(), y_lib.cpu().numpy())[1] <= 1e-4       # fused GEMM == library GEMM on decoded weights
     want_hits = torch.bincount(sel[rw != 0].reshape(-1), minlength=NE).tolist()
     assert hits.tolist() == want_hits
     ref = O.moe_ref([expert_to_oracle(e) for e in exs], levels, x.numpy(), sel.numpy(), rw.numpy())
