@@ -93,7 +93,7 @@ int nq_pf_combine(const float* y, const float* zd, const int32_t* pos, const int
  * pf_decode + grouped GEMM pair (sm120/moe.py:303-324, sm120/pf_gemm.py:7-34, sm120/nqmoe.cu:1013-1080); the dense fp16
  * weights are never materialised.
  *   nq_pf_plan   from per-expert pair counts (int32 [E], pairs sorted by expert) build the pass list on the device:
- *                a pass = one resident expert x up to 512 of its pairs.  plan: int32 [nq_pf_plan_ints(E, pairs)].
+ *                a pass = one resident expert x up to 448 of its pairs.  plan: int32 [nq_pf_plan_ints(E, pairs)].
  *   nq_pf_gemm   down = 0: acc_g[p] = xg[p] Wg^T, acc_u[p] = xu[p] Wu^T (act0 = xg, act1 = xu fp16 [pairs][H];
  *                out0 = acc_g, out1 = acc_u fp32 [pairs][I]); down = 1: y[p] = h[p] Wd^T (act0 = h fp16 [pairs][I],
  *                out0 = y fp32 [pairs][H], act1 / out1 unused).  Rows of pairs whose expert is not resident are not

@@ -3,16 +3,17 @@
 // Replaces the reference's prefill sequence pf_decode -> dense fp16 weights in VRAM -> cuBLAS / Triton grouped GEMM
 // (sm120/moe.py:303-324, sm120/pf_gemm.py, sm120/nqmoe.cu:1013-1080): the dense weights are never written to HBM.
 //
-// One work item = (pass, 128-row weight group): a pass is one expert and up to 512 of its tokens.  Per item a CTA
+// One work item = (pass, 128-row weight group): a pass is one expert and up to 448 of its tokens.  Per item a CTA
 // walks K in blocks of 64:
 //   warp 0        TMA: the tokens' activation tile [ntok x 64] fp16 (SWIZZLE_128B boxes of 64 rows) -> shared memory
 //   warps 2..17   decode: warp (h, s) streams strip s of the group with cp.async, decodes k-steps 4h..4h+3 of each unit
 //                 in registers (bit-exact fp16) and stores them as the UMMA A tile [128 x 64] (K-major, no swizzle) of
 //                 k-block 2 c + h
 //   warp 1        one thread issues tcgen05.mma (M 128 = weight rows, N = tokens, K 16) into a [128 x 512] fp32
-//                 accumulator in TMEM; tcgen05.commit frees the stage
+//                 accumulator in TMEM; tcgen05.commit frees the stages.  Token tiles run 2..4 k-blocks ahead
+//                 (as many stages as fit 120 KB), weight tiles 4 stages (two per decode half)
 //   warps 2..17   epilogue: tcgen05.ld the accumulator and store fp32 rows acc[pair][128 columns] (coalesced)
-// Each decoded weight is used for every token of the pass, so decode cost is paid once per expert (for up to 512
+// Each decoded weight is used for every token of the pass, so decode cost is paid once per expert (for up to 448
 // tokens).  Tensor-pipe bound by intent; the decode instruction rate is the practical limit.
 // Every mbarrier wait is bounded: on time-out the CTA raises status[0], drains and returns.
 #include <cuda.h>
@@ -23,14 +24,21 @@
 
 namespace nq {
 
-constexpr int kPfTokens = 512;                       // tokens per pass = TMEM columns
+// timing experiments only: 1 = decode warps skip the decode, 2 = no MMAs are issued (results are then wrong)
+#ifndef NQ_PF_DEBUG
+#define NQ_PF_DEBUG 0
+#endif
+constexpr int kPfTokens = 448;                       // tokens per pass (7 TMA boxes; the accumulator has 512 TMEM columns)
+constexpr int kPfTmemCols = 512;
 constexpr int kPfBoxRows = 64;                       // token rows per TMA box
+constexpr int kPfBoxBytes = kPfBoxRows * 128;        // [64 rows][64 k] fp16
+constexpr int kPfBBoxes = 15;                        // token-tile region: split into 2..4 stages of ceil(ntok / 64) boxes
+constexpr int kPfAStages = 4;                        // weight tiles: stages 0, 2 filled by decode half 0, stages 1, 3 by half 1
 constexpr int kPfABytes = 128 * 64 * 2;              // A tile of one k-block
-constexpr int kPfBBytes = kPfTokens * 64 * 2;        // token tile of one k-block
-constexpr int kPfRingDepth = 3;
+constexpr int kPfRingDepth = 2;
 constexpr int kPfDecodeWarps = 16;
 constexpr int kPfThreads = 32 * (2 + kPfDecodeWarps);
-constexpr int kPfSmem = 2 * kPfBBytes + 2 * kPfABytes + kPfDecodeWarps * kPfRingDepth * kStageBytes + 1024 + 256;
+constexpr int kPfSmem = kPfBBoxes * kPfBoxBytes + kPfAStages * kPfABytes + kPfDecodeWarps * kPfRingDepth * kStageBytes + 1024 + 256;
 constexpr unsigned long long kPfWaitNs = 2000000000ull;   // a wait that lasts 2 s is treated as a hang
 
 struct PfPass { int expert, row0, ntok, pad; };
@@ -159,15 +167,17 @@ __device__ __forceinline__ void decode_half(uint32_t* wb, uint32_t* wr, const Un
 
 struct PfShared
 {
-    uint64_t full_b[2], full_a[2], empty[2], acc_full, acc_empty;
+    uint64_t full_b[4], empty_b[4], full_a[kPfAStages], empty_a[kPfAStages], acc_full, acc_empty;
     uint32_t tmem_base;
     volatile int abort_flag;
 };
+// stages the token-tile region is cut into for a pass of nbox boxes per k-block
+__device__ __forceinline__ int b_stages(int nbox) { const int n = kPfBBoxes / nbox; return n > 4 ? 4 : n; }
 
 // one decode warp, one item: stream its strip over all chunks, fill the A tile of k-block 2 c + HALF for every chunk c.
 // `it` counts the k-blocks this warp has filled so far (phase of the stage barriers).  false = aborted.
 template <bool REFINED, int RC, int HALF>
-__device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int C, int NS, int nm, int lane, uint8_t* a_tile,
+__device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int C, int NS, int nm, int lane, uint8_t* a_tiles,
                                              uint8_t* ring, PfShared* sh, uint32_t& it)
 {
     unsigned long long fl = ~0ull;
@@ -212,13 +222,20 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
         const uint32_t sign2 = ((vb >> (lane >> 2)) & 1u) * 0x80008000u;
         const uint4 b = *(const uint4*)(st + lane * 16);
         uint32_t wb[6] = {b.x, b.y, b.z, b.w, 0u, 0u};
-        // the MMAs that read this stage two k-blocks ago must have completed (stage HALF is only ever filled by this half)
-        if (ok && !mbar_wait(&sh->empty[HALF], ((it >> 1) & 1u) ^ 1u, &sh->abort_flag)) ok = false;
+        // k-block `it` goes to stage it % 4 (always HALF or HALF + 2 for this warp); the MMAs that read that stage four
+        // k-blocks ago must have completed
+        const uint32_t sa = it % kPfAStages;
+        if (ok && !mbar_wait(&sh->empty_a[sa], ((it / kPfAStages) & 1u) ^ 1u, &sh->abort_flag)) ok = false;
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        const ATileSink<HALF> sink{a_tile + strip % 8 * 2048 + lane * 4};
+        const ATileSink<HALF> sink{a_tiles + sa * kPfABytes + strip % 8 * 2048 + lane * 4};
         bool refined = false;
         if constexpr (REFINED) refined = (fl >> ch) & 1ull;
+#if NQ_PF_DEBUG == 1
+        if (ok) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->full_a[sa]); }
+        if (false)
+#else
         if (ok)
+#endif
         {
             if (refined)
             {
@@ -231,7 +248,7 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
                 decode_half<false, 0, HALF>(wb, nullptr, consts_level2(sign2), lane, sink);
             fence_async_smem();                      // generic-proxy stores -> visible to the tensor core (async proxy)
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->full_a[HALF]);
+            if (lane == 0) mbar_arrive(&sh->full_a[sa]);
         }
         it += 2;
     }
@@ -241,9 +258,9 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
 
 template <int HALF>
 __device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int rc, int strip, int C, int NS, int nm, int lane,
-                                            uint8_t* a_tile, uint8_t* ring, PfShared* sh, uint32_t& it)
+                                            uint8_t* a_tiles, uint8_t* ring, PfShared* sh, uint32_t& it)
 {
-#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV, HALF>(P, strip, C, NS, nm, lane, a_tile, ring, sh, it)
+#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV, HALF>(P, strip, C, NS, nm, lane, a_tiles, ring, sh, it)
     if (level < 4) NQ_RUN(false, 0);
     switch (rc)
     {
@@ -267,22 +284,23 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* b_tiles = smem;                                  // 2 x [512 tokens][64 k] fp16, 128-byte swizzle (TMA)
-    uint8_t* a_tiles = smem + 2 * kPfBBytes;                  // 2 x [128 rows][64 k] fp16, core-matrix layout
-    uint8_t* rings = a_tiles + 2 * kPfABytes;                 // per decode warp: kPfRingDepth plane stages
+    uint8_t* b_tiles = smem;                                  // token tiles [rows][64 k] fp16, 128-byte swizzle (TMA boxes)
+    uint8_t* a_tiles = smem + kPfBBoxes * kPfBoxBytes;        // kPfAStages x [128 rows][64 k] fp16, core-matrix layout
+    uint8_t* rings = a_tiles + kPfAStages * kPfABytes;        // per decode warp: kPfRingDepth plane stages
     PfShared* sh = (PfShared*)(rings + kPfDecodeWarps * kPfRingDepth * kStageBytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0)
     {
-        for (int s = 0; s < 2; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->full_a[s], kPfDecodeWarps / 2); mbar_init(&sh->empty[s], 1); }
+        for (int s = 0; s < 4; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->empty_b[s], 1); }
+        for (int s = 0; s < kPfAStages; ++s) { mbar_init(&sh->full_a[s], kPfDecodeWarps / 2); mbar_init(&sh->empty_a[s], 1); }
         mbar_init(&sh->acc_full, 1); mbar_init(&sh->acc_empty, kPfDecodeWarps);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1)
     {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&sh->tmem_base)), "r"(kPfTokens) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&sh->tmem_base)), "r"(kPfTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -293,27 +311,29 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
     const int N = a.down ? a.H : 2 * a.I, K = a.down ? a.I : a.H, C = K / 128, NS = N / 16, groups = N / 128, nkb = K / 64;
     const int npass = a.plan[0], nitems = npass * groups;
     const PfPass* passes = (const PfPass*)(a.plan + 4);
-    uint32_t it = 0, nitem = 0;     // k-blocks / items handled so far by this role (barrier phases)
+    uint32_t it = 0, nitem = 0;     // k-blocks / items handled so far by this role (phases of the A-stage and accumulator barriers)
+    uint32_t used_b[4] = {0, 0, 0, 0};   // times each token-tile stage was used (its stage count changes from pass to pass)
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, ++nitem)
     {
         const int pi = item / groups, wg = item - pi * groups;
         const PfPass ps = passes[pi];
-        const int ntok16 = (ps.ntok + 15) & ~15, nbox = (ps.ntok + kPfBoxRows - 1) / kPfBoxRows;
+        const int ntok16 = (ps.ntok + 15) & ~15, nbox = (ps.ntok + kPfBoxRows - 1) / kPfBoxRows, nb = b_stages(nbox);
         const int up = !a.down && wg >= a.I / 128;
         if (warp == 0)
         {
-            // ---- token tiles by TMA
+            // ---- token tiles by TMA, up to nb k-blocks ahead of the MMAs
             if (lane == 0)
             {
                 const CUtensorMap* map = up ? &tmap1 : &tmap0;
-                for (int kb = 0; kb < nkb; ++kb, ++it)
+                for (int kb = 0; kb < nkb; ++kb)
                 {
-                    const int s = it & 1;
-                    if (!mbar_wait(&sh->empty[s], ((it >> 1) & 1u) ^ 1u, &sh->abort_flag)) break;
-                    mbar_expect_tx(&sh->full_b[s], (uint32_t)nbox * kPfBoxRows * 128);
+                    const int s = kb % nb;
+                    if (!mbar_wait(&sh->empty_b[s], (used_b[s] & 1u) ^ 1u, &sh->abort_flag)) break;
+                    ++used_b[s];
+                    mbar_expect_tx(&sh->full_b[s], (uint32_t)nbox * kPfBoxBytes);
                     for (int j = 0; j < nbox; ++j)
-                        tma_load_2d(b_tiles + s * kPfBBytes + j * kPfBoxRows * 128, map, kb * 64, ps.row0 + j * kPfBoxRows, &sh->full_b[s]);
+                        tma_load_2d(b_tiles + (s * nbox + j) * kPfBoxBytes, map, kb * 64, ps.row0 + j * kPfBoxRows, &sh->full_b[s]);
                 }
             }
         }
@@ -326,21 +346,27 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
                 tc_fence_after();
                 for (int kb = 0; ok && kb < nkb; ++kb, ++it)
                 {
-                    const int s = it & 1;
-                    const uint32_t ph = (it >> 1) & 1u;
-                    if (!mbar_wait(&sh->full_b[s], ph, &sh->abort_flag) || !mbar_wait(&sh->full_a[s], ph, &sh->abort_flag)) { ok = false; break; }
+                    const int s = kb % nb, sa = it % kPfAStages;
+                    if (!mbar_wait(&sh->full_b[s], used_b[s] & 1u, &sh->abort_flag) ||
+                        !mbar_wait(&sh->full_a[sa], (it / kPfAStages) & 1u, &sh->abort_flag)) { ok = false; break; }
+                    ++used_b[s];
                     tc_fence_after();
-                    const uint32_t abase = saddr(a_tiles + s * kPfABytes), bbase = saddr(b_tiles + s * kPfBBytes);
-                    for (int sub = 0; sub * 256 < ntok16; ++sub)
+                    const uint32_t abase = saddr(a_tiles + sa * kPfABytes), bbase = saddr(b_tiles + s * nbox * kPfBoxBytes);
+                    // N <= 256 per instruction: one MMA per k-step, or two of (nearly) equal width
+                    const int n0 = ntok16 <= 256 ? ntok16 : ((ntok16 / 2 + 15) & ~15);
+#if NQ_PF_DEBUG != 2
+                    for (int c0 = 0; c0 < ntok16; c0 += n0)
                     {
-                        const int n = ntok16 - sub * 256 < 256 ? ntok16 - sub * 256 : 256;
+                        const int n = ntok16 - c0 < n0 ? ntok16 - c0 : n0;
                         const uint32_t idesc = instr_desc(n);
 #pragma unroll
                         for (int k16 = 0; k16 < 4; ++k16)
-                            tc_mma_f16(tmem + sub * 256, smem_desc(abase + k16 * 256, 128, 1024, 0),
-                                       smem_desc(bbase + sub * 256 * 128 + k16 * 32, 16, 1024, 2), idesc, (kb | k16) != 0);
+                            tc_mma_f16(tmem + c0, smem_desc(abase + k16 * 256, 128, 1024, 0),
+                                       smem_desc(bbase + c0 * 128 + k16 * 32, 16, 1024, 2), idesc, (kb | k16) != 0);
                     }
-                    tc_commit(&sh->empty[s]);          // arrives when the MMAs above have read the stage
+#endif
+                    tc_commit(&sh->empty_a[sa]);       // both arrive when the MMAs above have read their operands
+                    tc_commit(&sh->empty_b[s]);
                 }
                 if (ok) tc_commit(&sh->acc_full);
             }
@@ -355,7 +381,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             const int rc = (int)row[10 + a.down], nm = a.down ? a.nm_dn : a.nm_gu;
             uint8_t* ring = rings + dw * kPfRingDepth * kStageBytes;
             uint32_t my_it = it + half;                 // this warp fills k-blocks 2 c + half
-            bool ok = half ? decode_item<1>(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, a_tiles + kPfABytes, ring, sh, my_it)
+            bool ok = half ? decode_item<1>(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, a_tiles, ring, sh, my_it)
                            : decode_item<0>(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, a_tiles, ring, sh, my_it);
             it += nkb;
             if (ok && lane == 0 && !mbar_wait(&sh->acc_full, nitem & 1u, &sh->abort_flag)) ok = false;
@@ -387,11 +413,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
     tc_fence_before();
     __syncthreads();
     if (warp == 1)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPfTokens) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPfTmemCols) : "memory");
 }
 
 // ---------------------------------------------------------------- pass plan (device side, no host sync)
-// counts[e] = routed pairs of expert e (pairs are sorted by expert).  A pass = one expert x up to 512 of its pairs;
+// counts[e] = routed pairs of expert e (pairs are sorted by expert).  A pass = one expert x up to 448 of its pairs;
 // experts at level 0 get none.  plan: [0] passes, [1] pairs covered, then PfPass records from int 4 on.
 __global__ void pf_plan_kernel(const int* __restrict__ counts, const int64_t* __restrict__ table, int E, int* plan, int max_passes)
 {
