@@ -154,6 +154,22 @@ typedef struct NqMoeForward {
 
 int nq_moe_forward(const NqMoeForward* args, void* stream);
 
+/* The same layer call for hosts that must not allocate - a plugin inside a serving engine that has already handed all
+ * device memory to its caches, or a process that bans allocator calls on its hot thread.  No counterpart in the reference
+ * (its workspaces are always torch tensors owned by the caller).  The workspaces of nq_moe_forward live in an array that
+ * is part of the library image: nq_moe_static_scratch_bytes() = 4 MiB, held by every GPU that loads the library until
+ * the process exits.  A call shape whose workspaces (nq_moe_workspace) do not fit is refused with NQ_ERR_ARG; 4 MiB
+ * covers the GLM-5 shape up to 4 tokens x top-8.  The call issues no cudaMalloc / cudaFree and no allocating library
+ * routine.  The first call on a device looks up the array's device address (cudaGetSymbolAddress): make that call at
+ * start-up, before any stream capture on the device.  All calls share the array, which keeps the previous call's
+ * contents; the counters are cleared at the start of each call, and calls that overlap on the GPU race - keep them in
+ * one stream order.  x fp16 [B][H], sel int64 [B][topk], rw fp16 [B][topk], table int64 [E][20], out fp32 [B][H];
+ * hits may be NULL. */
+size_t nq_moe_static_scratch_bytes(void);
+int nq_moe_forward_static(const void* x, const int64_t* sel, const void* rw, const int64_t* table, float* out,
+                          int B, int topk, int E, int H, int I, int nm_gu, int nm_dn, int ks_gu, int ks_dn,
+                          int32_t* hits, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -51,6 +51,8 @@ SIGNATURES = {
     "nq_pf_gemm": (_i, [_p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p]),
     "nq_moe_workspace": (_i, [_i, _i, _i, _i, _i, _i, C.POINTER(NqMoeWorkspace)]),
     "nq_moe_forward": (_i, [C.POINTER(NqMoeForward), _p]),
+    "nq_moe_static_scratch_bytes": (_sz, []),
+    "nq_moe_forward_static": (_i, [_p, _p, _p, _p, _p] + [_i] * 9 + [_p, _p]),
 }
 
 _lib = None

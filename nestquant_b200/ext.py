@@ -166,3 +166,16 @@ def moe_forward(x, sel, rw, table, out, acc_gu, h, acc_d, cnt_gu, cnt_d, wq, I, 
     a.nm_gu, a.nm_dn, a.ks_gu, a.ks_dn = nm_gu, nm_dn, int(cfg_gu[0]), int(cfg_dn[0])
     a.G, a.force_level, a.which = G, force_level, which
     check(lib().nq_moe_forward(C.byref(a), current_stream()), "moe_forward")
+
+
+def moe_forward_static(x, sel, rw, table, out, I, nm_gu, nm_dn, ks_gu, ks_dn, hits_ptr=0):
+    """moe_forward for hosts that must not allocate (a plugin inside an engine that owns all device memory, a thread
+    that may not call the allocator): the workspaces come from a 4 MiB array built into the library, shared by every
+    call on the device.  Raises if the call shape needs more; calls that overlap on the GPU race on the array."""
+    _need(x, torch.float16, "x"); _need(rw, torch.float16, "rw"); _need(sel, torch.int64, "sel")
+    _need(table, torch.int64, "table"); _need(out, torch.float32, "out")
+    if x.dim() != 2 or sel.dim() != 2 or sel.shape[0] != x.shape[0] or rw.shape != sel.shape or out.numel() < x.numel():
+        raise NestQuantError("moe_forward_static: x [B,H], sel [B,topk], rw [B,topk], out [B,H]")
+    check(lib().nq_moe_forward_static(ptr(x), ptr(sel), ptr(rw), ptr(table), ptr(out), x.shape[0], sel.shape[1], table.shape[0],
+                                      x.shape[1], I, nm_gu, nm_dn, ks_gu, ks_dn, hits_ptr or None, current_stream()),
+          "moe_forward_static")
