@@ -63,6 +63,15 @@ int nq_pf_decode(const int64_t* table, const int32_t* experts, int n_experts, vo
 int nq_mailbox(int64_t* table, const int64_t* stage, const int32_t* seq, int32_t* applied, int32_t* applied_host,
                int E, void* stream);
 
+/* Promotion (level 2 -> 4) or demotion of one expert, enqueued on a side stream: copy the pinned host record (the
+ * expert's residual planes, see nestquant_b200/p4rec.py) into its slot, then the new table row into stage[e], then the
+ * new sequence number into seq[e] - three copies in stream order, so the row is never visible before its bytes.  A
+ * demotion passes slot = host_record = NULL.  The compute stream's next nq_mailbox applies the row.  All host buffers
+ * must be pinned and must stay valid until the stream has executed the copies; one outstanding operation per expert.
+ * Replaces Engine::issue_copies (streaming/nqstream.cu:183-191). */
+int nq_promote(void* slot, const void* host_record, size_t record_bytes, int64_t* stage_row, const int64_t* host_row,
+               int32_t* seq_entry, const int32_t* host_seq, void* stream);
+
 /* ---- prefill path: stream-ordered helpers around the grouped GEMMs ---------------------------------------------
  * Pairs = (token, expert) picks sorted by expert: pt[p] = token, pe[p] = expert, prw[p] = routing weight (fp16).
  * R = number of pairs in this call.  z arrays are fp32 [R][4] (low-rank inputs, rank <= 4). */

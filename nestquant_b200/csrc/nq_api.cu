@@ -72,3 +72,22 @@ int nq_mailbox(int64_t* table, const int64_t* stage, const int32_t* seq, int32_t
 }
 
 }  // extern "C"
+
+// Promotion / demotion of one expert: bytes, then the staged table row, then the sequence number, in that order on one
+// (side) stream, so the row can never become visible before the bytes it points at.  The next nq_mailbox on the compute
+// stream picks the row up.  Host buffers must be pinned and stay untouched until the stream has passed the copies.
+extern "C" int nq_promote(void* slot, const void* host_record, size_t record_bytes, int64_t* stage_row, const int64_t* host_row,
+                          int32_t* seq_entry, const int32_t* host_seq, void* stream)
+{
+    NQ_REQUIRE(stage_row && host_row && seq_entry && host_seq, "nq_promote: null row or sequence pointer");
+    NQ_REQUIRE(!(slot || host_record || record_bytes) || (slot && host_record && record_bytes),
+               "nq_promote: slot, record and its size must be given together (or none of them for a demotion)");
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaSuccess;
+    if (slot && host_record && record_bytes)
+        e = cudaMemcpyAsync(slot, host_record, record_bytes, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(stage_row, host_row, sizeof(int64_t) * nq::kTableWidth, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(seq_entry, host_seq, sizeof(int32_t), cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return nq::fail(NQ_ERR_CUDA, "nq_promote: %s", cudaGetErrorString(e));
+    return NQ_OK;
+}
