@@ -209,17 +209,6 @@ def main():
     cfg, bias, beta, levels, local, owned = workload(world, rank)
     E, topk, H, I = cfg["E"], cfg["topk"], cfg["H"], cfg["I"]
     L, experts = synth.build_layer(cfg, local, seed=SEED, dev=dev, Bmax=4, owned=owned)
-    total = args.warmup + args.steps
-    sels, rws, xs, nbytes, nbytes_gu = [], [], [], [], []
-    for step in range(total):
-        sel, rw = synth.routing(1, E, topk, SEED + 1 + step, bias, beta)
-        sels.append(sel.to(dev)); rws.append(rw.to(dev)); xs.append(synth.tokens(1, H, SEED + 7 + step))
-        act = [e for e in set(sel.reshape(-1).tolist()) if local[e] > 0]
-        nbytes.append(sum(experts[e].bytes(local[e]) + (3 * H + 3 * I) * 2 for e in act))
-        nbytes_gu.append(sum(experts[e].gu.nbytes(local[e]) + (2 * H + 2 * I) * 2 for e in act))
-    xd = [x.to(dev) for x in xs]
-    xh = [x.pin_memory() for x in xs]
-    out_h = torch.empty(1, H, dtype=torch.float32).pin_memory()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
@@ -229,64 +218,119 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def layer(i, x):
-        out = L(x, sels[i], rws[i])
+    def allmax(t):
         if world > 1:
-            dist.all_reduce(out)
-        return out
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t
 
-    # ---- device-resident timing: one event pair per step, L2 flushed (untimed) between steps
-    for i in range(args.warmup):
-        flush.zero_(); layer(i, xd[i])
-    barrier()
-    pairs = []
-    with ClockSampler(local_rank) as clk:
-        t_wall = time.perf_counter()
-        for i in range(args.warmup, total):
-            flush.zero_()
-            a, b = ev(), ev()
-            a.record(); layer(i, xd[i]); b.record()
-            pairs.append((a, b))
+    def decode_case(B, steps, warmup, seed_off, want_kernel, want_e2e):
+        """B tokens per step; returns dict(us_total, bytes_total, [k_us, k_bytes], [e2e_us], clocks)"""
+        total = warmup + steps
+        sels, rws, xs, nbytes, nbytes_gu, sel_h, rw_h = [], [], [], [], [], [], []
+        for step in range(total):
+            sel, rw = synth.routing(B, E, topk, SEED + seed_off + step, bias, beta)
+            sel_h.append(sel); rw_h.append(rw)
+            sels.append(sel.to(dev)); rws.append(rw.to(dev)); xs.append(synth.tokens(B, H, SEED + seed_off + 7000 + step))
+            act = [e for e in set(sel.reshape(-1).tolist()) if local[e] > 0]
+            nbytes.append(sum(experts[e].bytes(local[e]) + (3 * H + 3 * I) * 2 for e in act))
+            nbytes_gu.append(sum(experts[e].gu.nbytes(local[e]) + (2 * H + 2 * I) * 2 for e in act))
+        xd = [x.to(dev) for x in xs]
+
+        def layer(i, x):
+            out = L(x, sels[i], rws[i])
+            if world > 1:
+                dist.all_reduce(out)
+            return out
+
+        r = {}
+        # device-resident timing: one event pair per step, L2 flushed (untimed) between steps
+        for i in range(warmup):
+            flush.zero_(); layer(i, xd[i])
         barrier()
-        t_wall = time.perf_counter() - t_wall
-    us = torch.tensor([a.elapsed_time(b) * 1e3 for a, b in pairs], dtype=torch.float64, device=dev)
-    by = torch.tensor(nbytes[args.warmup:], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(us, op=dist.ReduceOp.MAX); dist.all_reduce(by, op=dist.ReduceOp.SUM)
-    us_total, by_total = float(us.sum()), float(by.sum())
+        pairs = []
+        with ClockSampler(local_rank) as clk:
+            for i in range(warmup, total):
+                flush.zero_()
+                a, b = ev(), ev()
+                a.record(); layer(i, xd[i]); b.record()
+                pairs.append((a, b))
+            barrier()
+        us = allmax(torch.tensor([a.elapsed_time(b) * 1e3 for a, b in pairs], dtype=torch.float64, device=dev))
+        by = torch.tensor(nbytes[warmup:], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(by, op=dist.ReduceOp.SUM)
+        r.update(us_total=float(us.sum()), bytes_total=float(by.sum()), clocks=clk.summary(), xs=xs, sel_h=sel_h, rw_h=rw_h, nbytes=nbytes)
+        if want_kernel:
+            # dominant kernel alone (gate|up GEMV): (route + gate|up) minus (route)
+            k = []
+            for i in range(warmup, total):
+                flush.zero_()
+                a, b, c = ev(), ev(), ev()
+                a.record(); L(xd[i], sels[i], rws[i], which=0); b.record(); L(xd[i], sels[i], rws[i], which=1); c.record()
+                k.append((a, b, c))
+            torch.cuda.synchronize()
+            r["k_us"] = sum(max(b.elapsed_time(c) - a.elapsed_time(b), 0.0) * 1e3 for a, b, c in k)
+            r["k_bytes"] = float(sum(nbytes_gu[warmup:]))
+        if want_e2e:
+            # end to end through the public API from HOST buffers: host -> pinned -> device, layer, device -> host, all
+            # inside one captured graph per call (what a serving engine does around this layer)
+            G = L.capture(B, host_io=True)
+            e2 = []
+            for i in range(total):
+                flush.zero_(); torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                G.x_host.copy_(xs[i]); G.sel_host.copy_(sel_h[i]); G.rw_host.copy_(rw_h[i])
+                G.replay()
+                if world > 1:
+                    dist.all_reduce(G.out)
+                    G.out_host.copy_(G.out, non_blocking=True)
+                torch.cuda.synchronize()
+                if i >= warmup:
+                    e2.append((time.perf_counter() - t0) * 1e6)
+            r["e2e_us"] = float(allmax(torch.tensor(e2, dtype=torch.float64, device=dev)).sum())
+        return r
 
-    # ---- dominant kernel alone (gate|up GEMV): event pairs around which = 1 calls (route + gate|up), minus the route kernel
-    k_us, r_us = [], []
-    for i in range(args.warmup, total):
-        flush.zero_()
-        a, b, c = ev(), ev(), ev()
-        a.record(); L(xd[i], sels[i], rws[i], which=0); b.record(); L(xd[i], sels[i], rws[i], which=1); c.record()
-        k_us.append((a, b, c))
-    torch.cuda.synchronize()
-    gu_us = sum(max(b.elapsed_time(c) - a.elapsed_time(b), 0.0) * 1e3 for a, b, c in k_us)
-    gu_bytes = float(sum(nbytes_gu[args.warmup:]))
+    # headline: 1 token per step
+    r1 = decode_case(1, args.steps, args.warmup, 1, True, True)
+    # MTP verify case of the same workload: 4 tokens per step (fewer steps)
+    s4 = max(8, args.steps // 4)
+    r4 = decode_case(4, s4, 3, 50001, False, False)
 
-    # ---- end to end through the public API with host buffers
-    for i in range(args.warmup):
-        L(xh[i].to(dev, non_blocking=True), sels[i], rws[i])
+    # prefill case (config 3): 8192 tokens, every resident expert at level 4, tokens sharded over the ranks
+    del L, experts
+    torch.cuda.empty_cache()
+    from nestquant_b200.ep import EPLayer
+    T_pf = 8192
+    own = set(owned)
+    Lp, _ = synth.build_layer(cfg, [4 if e in own else 0 for e in range(E)], seed=SEED + 1, dev=dev, Bmax=1, owned=owned)
+    ep = EPLayer(Lp, rank, world) if world > 1 else None
+    Tl = T_pf // world
+    selp, rwp = synth.routing(T_pf, E, topk, SEED + 99)
+    xp = synth.tokens(T_pf, H, SEED + 98)
+    xp, selp, rwp = (t[rank * Tl:(rank + 1) * Tl].to(dev) for t in (xp, selp, rwp))
+    run_pf = (lambda: ep.prefill(xp, selp, rwp)) if world > 1 else (lambda: Lp.prefill(xp, selp, rwp))
+    for _ in range(2):
+        run_pf()
     barrier()
-    e2e_us = []
-    for i in range(args.warmup, total):
-        flush.zero_(); torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        out = layer(i, xh[i].to(dev, non_blocking=True))
-        out_h.copy_(out, non_blocking=True)
-        torch.cuda.synchronize()
-        e2e_us.append((time.perf_counter() - t0) * 1e6)
-    e2 = torch.tensor(e2e_us, dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(e2, op=dist.ReduceOp.MAX)
-    e2e_total = float(e2.sum())
+    pf = []
+    for _ in range(5):
+        a, b = ev(), ev()
+        a.record(); run_pf(); b.record()
+        pf.append((a, b))
+    barrier()
+    pf_ms = float(allmax(torch.tensor([a.elapsed_time(b) for a, b in pf], dtype=torch.float64, device=dev)).median())
+    pf_flops = 2.0 * T_pf * topk * 3 * H * I
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
+        tpeak = 1689.3
+        try:
+            tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+        except Exception:
+            pass
+        us_total, by_total = r1["us_total"], r1["bytes_total"]
         value = by_total / us_total / 1e3
-        achieved = gu_bytes / gu_us / 1e3
+        achieved = r1["k_bytes"] / r1["k_us"] / 1e3
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": us_total / args.steps / 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f16", "data": "synthetic",
@@ -294,24 +338,33 @@ def main():
                            "level4_experts": N_LEVEL4, "level4_pick_share": round(synth.share_at_level4(levels, bias, beta, E, topk), 3),
                            "tokens_per_step": 1, "parallelism": f"ep{world}", "l2": "flushed between steps (256 MB write)"},
                 "layer_us": us_total / args.steps, "bytes_per_step": by_total / args.steps,
-                "e2e": {"value": by_total / e2e_total / 1e3, "unit": UNIT, "h2d_bytes_per_step": H * 2,
-                        "d2h_bytes_per_step": H * 4, "layer_us": e2e_total / args.steps},
+                "e2e": {"value": by_total / r1["e2e_us"] / 1e3, "unit": UNIT, "h2d_bytes_per_step": H * 2 + topk * 10,
+                        "d2h_bytes_per_step": H * 4, "layer_us": r1["e2e_us"] / args.steps,
+                        "how": "host buffers -> pinned staging -> one CUDA-graph replay (H2D copies, 3 kernels, D2H copy) -> synchronize"},
                 "gpu_launches": 3 * args.steps,
                 "roofline": {"kernel": "gemv_kernel<0> (gate|up GEMV + SwiGLU)", "bound": "hbm", "achieved": achieved, "peak": peak,
                              "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind + " copy bandwidth",
-                             "frac_of_nominal_8000": achieved / 8000.0, "us_per_launch": gu_us / args.steps,
-                             "bytes_per_launch": gu_bytes / args.steps,
-                             "traffic": NCU_TRAFFIC_RATIO * gu_bytes / args.steps},
-                "clocks": clk.summary()}
+                             "frac_of_nominal_8000": achieved / 8000.0, "us_per_launch": r1["k_us"] / args.steps,
+                             "bytes_per_launch": r1["k_bytes"] / args.steps,
+                             "traffic": NCU_TRAFFIC_RATIO * r1["k_bytes"] / args.steps},
+                "decode_4tok": {"layer_us": r4["us_total"] / s4, "value": r4["bytes_total"] / r4["us_total"] / 1e3, "unit": UNIT,
+                                "bytes_per_step": r4["bytes_total"] / s4, "steps": s4},
+                "prefill": {"workload": "8192 tokens x top-8, all experts level 4", "ms": pf_ms, "tflops": pf_flops / pf_ms / 1e9,
+                            "frac_of_measured_tensor_peak": pf_flops / pf_ms / 1e9 / tpeak, "frac_of_nominal_2250": pf_flops / pf_ms / 1e9 / 2250.0,
+                            "parallelism": f"ep{world}" + (" all-to-all dispatch/combine" if world > 1 else "")},
+                "clocks": r1["clocks"]}
         # CPU baseline: the oracle port on one full step (rank 0, N = 1 only)
         if world == 1:
             from oracle import nq_oracle as O
             from tests.util import expert_to_oracle
+            from nestquant_b200 import moe
             i = args.warmup
-            act = sorted(set(sels[i].reshape(-1).tolist()))
-            exs = {e: expert_to_oracle(experts[e]) for e in act}
-            ref_us = oracle_step(exs, levels, xs[i].numpy(), sels[i].cpu().numpy(), rws[i].cpu().numpy()) * 1e6
-            line["cpu_baseline"] = {"value": nbytes[i] / ref_us / 1e3, "unit": UNIT, "cores": O.lib().nqo_threads(), "kind": "port",
+            sel_host, rw_host = r1["sel_h"], r1["rw_h"]
+            act = sorted(set(sel_host[i].reshape(-1).tolist()))
+            exs = {e: expert_to_oracle(moe.Expert(H, I, seed=SEED * 100003 + e, dev="cpu", rk_gu=0, rk_dn=7, var=True, sv=0.02))
+                   for e in act}
+            ref_us = oracle_step(exs, levels, r1["xs"][i].numpy(), sel_host[i].numpy(), rw_host[i].numpy()) * 1e6
+            line["cpu_baseline"] = {"value": r1["nbytes"][i] / ref_us / 1e3, "unit": UNIT, "cores": O.lib().nqo_threads(), "kind": "port",
                                     "sample": "one full 1-token step (8 experts: dense decode + fp32 matmuls)", "layer_us": ref_us}
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -310,6 +310,43 @@ class MoELayer:
         return out
 
 
+    def capture(s, B, with_mailbox=None, host_io=False):
+        """Capture one B-token layer call in a CUDA graph over static buffers and return the handle:
+        .x [B,H] fp16, .sel [B,topk] int64, .rw [B,topk] fp16, .out [B,H] fp32 (device), .replay().
+        with_mailbox: a Mailbox whose apply() is captured in front of the layer.  host_io=True adds pinned host mirrors
+        (.x_host, .sel_host, .rw_host, .out_host) and captures the host->device / device->host copies too, so one replay
+        is a complete call from host buffers."""
+        dev = s.table.device
+        g = _Captured()
+        g.x = torch.zeros(B, s.H, dtype=torch.float16, device=dev)
+        g.sel = torch.zeros(B, s.topk, dtype=torch.int64, device=dev)
+        g.rw = torch.zeros(B, s.topk, dtype=torch.float16, device=dev)
+        g.out = torch.zeros(B, s.H, dtype=torch.float32, device=dev)
+        if host_io:
+            g.x_host, g.sel_host, g.rw_host = g.x.cpu().pin_memory(), g.sel.cpu().pin_memory(), g.rw.cpu().pin_memory()
+            g.out_host = g.out.cpu().pin_memory()
+
+        def body():
+            if host_io:
+                g.x.copy_(g.x_host, non_blocking=True); g.sel.copy_(g.sel_host, non_blocking=True); g.rw.copy_(g.rw_host, non_blocking=True)
+            if with_mailbox is not None:
+                with_mailbox.apply()
+            s(g.x, g.sel, g.rw, out=g.out)
+            if host_io:
+                g.out_host.copy_(g.out, non_blocking=True)
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                body()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        g.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g.graph):
+            body()
+        return g
+
     def prefill(s, x, sel, rw, out=None, R=None, G=None, table=None, deterministic=True, fused=True):
         """T > Bmax tokens: every routed expert decoded once (level read from the live table row), grouped GEMMs with fp32
         outputs, same math as __call__.  x fp16 [T,H], sel int64 [T,topk], rw fp16 [T,topk] -> fp32 [T,H].
@@ -401,6 +438,14 @@ class MoELayer:
         if deterministic:
             M.pf_combine(y_all, zd_all, pos, sel, rw, tb, out, I)
         return out
+
+
+class _Captured:
+    """static buffers + CUDA graph of one captured layer call (MoELayer.capture)"""
+
+    def replay(s):
+        s.graph.replay()
+        return s.out
 
 
 class Mailbox:
