@@ -52,9 +52,10 @@ struct MoeArgs
     float* part_gu;    // [ks_gu][S][2I]
     __half* h;         // [S][I]
     float* part_d;     // [ks_dn][S][H]
-    int* cnt_gu;       // [S * I/128] arrival counters, zero on entry and exit
+    int* cnt_gu;       // [2 * S * I/128] arrival counters ((run, group), then (run, 512-block)), zero on entry and exit
     int* cnt_d;        // [H/128]
     int* wq;           // [4] work / exit counters, zero on entry and exit
+    float* zd;         // [S][I/128][4] down low-rank partials (gate|up kernel writes, down kernel reads)
     float* out;        // [B][H]
     int* hits;         // optional [E] pick counters (may be host-mapped)
 };
@@ -358,13 +359,31 @@ __global__ void __launch_bounds__(256, NQ_GEMV_MINBLOCKS) gemv_kernel(MoeArgs a)
 
         if constexpr (DOWN == 0)
         {
-            // (run, group) complete: WHT128, sv, SwiGLU, su_d, WHT128 -> h.  One warp per token.
+            // (run, group) complete: WHT128, sv, (+ low rank), SwiGLU, su_d, WHT128 -> h.  One warp per token.
             const __half* scales = (const __half*)row[9];
             const __half *sv_g = scales + a.H, *sv_u = sv_g + a.I, *su_d = sv_u + a.I;
-            const int col = grp * 128 + lane * 4;
+            const __half* lr = (const __half*)row[14];
+            const int rg = lr ? (int)row[16] : 0, rd = lr ? (int)row[17] : 0, hw = (int)row[18];
+            const __half* lr4 = level == 4 ? (const __half*)row[15] : nullptr;
+            const int col = grp * 128 + lane * 4, ng = a.I / 128;
             for (int j = warp; j < ntok; j += 8)
             {
                 const int slot = run.slot[j];
+                float z[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int r = 0; r < rg; ++r)          // z = x V_gu^T on the unrotated input
+                {
+                    const __half* xr = a.x + (size_t)(slot / a.topk) * a.H;
+                    float d = 0.f;
+                    for (int k = lane * 4; k < a.H; k += 128)
+                    {
+                        float f[4], w[4];
+                        load4h(xr + k, f); load4h(lr + (size_t)r * a.H + k, w);
+                        d += f[0] * w[0] + f[1] * w[1] + f[2] * w[2] + f[3] * w[3];
+                    }
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                    z[r] = d;
+                }
                 float gu[2][4];
 #pragma unroll
                 for (int u = 0; u < 2; ++u)
@@ -378,14 +397,73 @@ __global__ void __launch_bounds__(256, NQ_GEMV_MINBLOCKS) gemv_kernel(MoeArgs a)
                     wht128(v, lane);
                     load4h((u ? sv_u : sv_g) + col, sc);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) gu[u][i] = v[i] * sc[i];
+                    for (int i = 0; i < 4; ++i) v[i] *= sc[i];
+                    for (int r = 0; r < rg; ++r)
+                    {
+                        float u2[4], u4[4] = {0.f, 0.f, 0.f, 0.f};
+                        const size_t o = (size_t)(u * rg + r) * a.I + col;
+                        load4h(lr + (size_t)rg * a.H + o, u2);
+                        if (lr4) load4h(lr4 + o, u4);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) v[i] += z[r] * u2[i] + z[r] * u4[i];
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) gu[u][i] = v[i];
                 }
                 float v[4], sc[4];
                 load4h(su_d + col, sc);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) v[i] = gu[0][i] / (1.f + __expf(-gu[0][i])) * gu[1][i] * sc[i];
+                for (int i = 0; i < 4; ++i) v[i] = silu(gu[0][i]) * gu[1][i];
+                for (int r = 0; r < rd; ++r)          // this group's share of z_dn = sw V_dn^T
+                {
+                    float w[4];
+                    load4h(lr + (size_t)rg * a.H + 2 * (size_t)rg * a.I + (size_t)r * a.I + col, w);
+                    float d = v[0] * w[0] + v[1] * w[1] + v[2] * w[2] + v[3] * w[3];
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                    if (lane == 0) a.zd[((size_t)slot * ng + grp) * 4 + r] = d;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] *= sc[i];
                 wht128(v, lane);
-                store4h(a.h + (size_t)slot * a.I + col, v);
+                if (hw <= 128) store4h(a.h + (size_t)slot * a.I + col, v);
+                else __stcg((float4*)(a.part_gu + (size_t)slot * N + col), make_float4(v[0], v[1], v[2], v[3]));   // fp32 stage: gate columns, k-slice 0
+            }
+            if (hw > 128)
+            {
+                // 512-wide rotation = H_4 (x) WHT128 / 2: the last of the hw/128 groups of a block combines their fp32 results
+                const int nb = hw / 128, b0 = grp / nb * nb;
+                __threadfence();
+                __syncthreads();
+                if (threadIdx.x == 0)
+                {
+                    int prev;
+                    int* ch = a.cnt_gu + S * ng + r * ng + b0;
+                    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(ch) : "memory");
+                    s_last = prev == nb - 1;
+                    if (s_last) *ch = 0;
+                }
+                __syncthreads();
+                if (s_last)
+                {
+                    __threadfence();
+                    const float rs = rsqrtf((float)nb);
+                    for (int task = warp; task < ntok * nb; task += 8)
+                    {
+                        const int j = task / nb, ob = task - j * nb, slot = run.slot[j];
+                        const float* p = a.part_gu + (size_t)slot * N + b0 * 128 + lane * 4;
+                        float o[4] = {0.f, 0.f, 0.f, 0.f};
+                        for (int b = 0; b < nb; ++b)
+                        {
+                            const float4 f = __ldcg((const float4*)(p + b * 128));
+                            const float sg = (__popc(ob & b) & 1) ? -1.f : 1.f;
+                            o[0] += sg * f.x; o[1] += sg * f.y; o[2] += sg * f.z; o[3] += sg * f.w;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) o[i] *= rs;
+                        store4h(a.h + (size_t)slot * a.I + (b0 + ob) * 128 + lane * 4, o);
+                    }
+                }
             }
         }
         else
@@ -411,7 +489,28 @@ __global__ void __launch_bounds__(256, NQ_GEMV_MINBLOCKS) gemv_kernel(MoeArgs a)
                     wht128(v, lane);
                     load4h(sv_o + col, sc);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) o[i] += w * (v[i] * sc[i]);
+                    for (int i = 0; i < 4; ++i) v[i] *= sc[i];
+                    const int64_t* erow = a.table + (int64_t)e * kTableWidth;
+                    const __half* lr = (const __half*)erow[14];
+                    const int rd = lr ? (int)erow[17] : 0;
+                    if (rd)
+                    {
+                        const int rg = (int)erow[16], ng = a.I / 128;
+                        const __half* lr4 = lv == 4 ? (const __half*)erow[15] : nullptr;
+                        const size_t ou = (size_t)rg * a.H + 2 * (size_t)rg * a.I + (size_t)rd * a.I;
+                        for (int r = 0; r < rd; ++r)
+                        {
+                            float z = 0.f;
+                            for (int gq = 0; gq < ng; ++gq) z += __ldcg(a.zd + ((size_t)s * ng + gq) * 4 + r);
+                            float u2[4], u4[4] = {0.f, 0.f, 0.f, 0.f};
+                            load4h(lr + ou + (size_t)r * a.H + col, u2);
+                            if (lr4) load4h(lr4 + 2 * (size_t)rg * a.I + (size_t)r * a.H + col, u4);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) v[i] += z * u2[i] + z * u4[i];
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[i] += w * v[i];
                 }
                 *(float4*)(a.out + (size_t)b * a.H + col) = make_float4(o[0], o[1], o[2], o[3]);
             }
@@ -452,7 +551,7 @@ int nq_moe_workspace(int B, int topk, int H, int I, int ks_gu, int ks_dn, NqMoeW
     w->acc_gu_floats = (size_t)ks_gu * S * 2 * I;
     w->h_halves = S * I + S * 2 * H;                    // h [S][I], then the rotated inputs [S][2][H]
     w->acc_d_floats = (size_t)ks_dn * S * H;
-    w->cnt_gu_ints = S * (I / 128);
+    w->cnt_gu_ints = 2 * S * (I / 128);
     w->cnt_d_ints = H / 128;
     w->wq_ints = 4;
     w->zd_floats = S * (I / 128) * 4;
@@ -467,11 +566,12 @@ int nq_moe_forward(const NqMoeForward* p, void* stream)
     NqMoeWorkspace need;
     const int rc = nq_moe_workspace(p->B, p->topk, p->H, p->I, p->ks_gu, p->ks_dn, &need);
     if (rc) return rc;
-    NQ_REQUIRE(p->x && p->sel && p->rw && p->table && p->out && p->acc_gu && p->h && p->acc_d && p->cnt_gu && p->cnt_d && p->wq && p->cnt_h,
+    NQ_REQUIRE(p->x && p->sel && p->rw && p->table && p->out && p->acc_gu && p->h && p->acc_d && p->cnt_gu && p->cnt_d && p->wq && p->cnt_h && p->zd,
                "nq_moe_forward: null tensor");
     NQ_REQUIRE(p->E > 0, "nq_moe_forward: E = %d", p->E);
     NQ_REQUIRE(p->acc_gu_floats >= need.acc_gu_floats && p->h_halves >= need.h_halves && p->acc_d_floats >= need.acc_d_floats &&
-               p->cnt_gu_ints >= need.cnt_gu_ints && p->cnt_d_ints >= need.cnt_d_ints && p->wq_ints >= need.wq_ints && p->cnt_h_ints >= need.cnt_h_ints,
+               p->cnt_gu_ints >= need.cnt_gu_ints && p->cnt_d_ints >= need.cnt_d_ints && p->wq_ints >= need.wq_ints && p->cnt_h_ints >= need.cnt_h_ints &&
+               p->zd_floats >= need.zd_floats,
                "nq_moe_forward: workspace too small (see nq_moe_workspace)");
     NQ_REQUIRE(p->out_floats >= (size_t)p->B * p->H, "nq_moe_forward: out too small");
     NQ_REQUIRE(nq::aligned16(p->x) && nq::aligned16(p->out) && nq::aligned16(p->acc_gu) && nq::aligned16(p->acc_d) && nq::aligned16(p->h),
@@ -482,7 +582,7 @@ int nq_moe_forward(const NqMoeForward* p, void* stream)
     a.B = p->B; a.topk = p->topk; a.E = p->E; a.H = p->H; a.I = p->I; a.nm_gu = p->nm_gu; a.nm_dn = p->nm_dn;
     a.force_level = p->force_level; a.ks_gu = p->ks_gu; a.ks_dn = p->ks_dn; a.table = p->table;
     a.route = p->cnt_h; a.h = (__half*)p->h; a.xrot = a.h + (size_t)p->B * p->topk * p->I;
-    a.part_gu = p->acc_gu; a.part_d = p->acc_d; a.cnt_gu = p->cnt_gu; a.cnt_d = p->cnt_d; a.wq = p->wq; a.out = p->out; a.hits = p->hits;
+    a.part_gu = p->acc_gu; a.part_d = p->acc_d; a.zd = p->zd; a.cnt_gu = p->cnt_gu; a.cnt_d = p->cnt_d; a.wq = p->wq; a.out = p->out; a.hits = p->hits;
     cudaStream_t st = (cudaStream_t)stream;
     const int S = p->B * p->topk;
     nq::route_kernel<<<S, 256, 0, st>>>(a);

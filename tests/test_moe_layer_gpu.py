@@ -60,6 +60,31 @@ def test_golden_layer():
     assert not y[4].any()                    # token routed only to a level-0 expert
 
 
+def test_golden_layer_with_low_rank_and_wide_rotation():
+    """decode path on the reference-generated layer with the low-rank plane (ranks 2/1 and 1/3) and a 512-wide
+    down-input rotation; mirrors sm120/check_lr.py: with the plane removed the result must be plainly wrong"""
+    from nestquant_b200 import moe
+    g = layer_from("layer_lr.npz")
+    L = moe.MoELayer(g["E"], g["H"], g["I"], Bmax=4, topk=g["topk"], ksplit=(2, 2))
+    keep = [expert_to_device(eo) for eo in g["experts"]]
+    for e, ex in enumerate(keep):
+        L.set(e, ex, g["levels"][e])
+    x, sel, rw = torch.from_numpy(g["x"].copy()).cuda(), torch.from_numpy(g["sel"]).cuda(), torch.from_numpy(g["rw"].copy()).cuda()
+    for ks in ([1], [2]):
+        y = L(x, sel, rw, cfg_gu=ks, cfg_dn=ks).clone()
+        torch.cuda.synchronize()
+        ma, rl = layer_errors(y.cpu().numpy(), g["out"])
+        assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL and rl <= 5e-4, (ks, ma, rl)
+    assert int(L.cnt_gu.abs().sum()) == 0
+    for ex in keep:
+        ex.lr = ex.lr4 = None
+    for e, ex in enumerate(keep):
+        L.set(e, ex, g["levels"][e])
+    y0 = L(x, sel, rw)
+    torch.cuda.synchronize()
+    assert layer_errors(y0.cpu().numpy(), g["out"])[1] > 20 * max(rl, 1e-6)
+
+
 @pytest.mark.parametrize("H,I", [(1024, 512), (768, 384)])
 def test_mixed_levels_vs_oracle(H, I):
     """12 experts, levels 2/4/0, three masked (50 % of chunks refined), production window codes and signs"""
