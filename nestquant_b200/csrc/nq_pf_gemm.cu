@@ -6,9 +6,9 @@
 // One work item = (pass, 128-row weight group): a pass is one expert and up to 448 of its tokens.  Per item a CTA
 // walks K in blocks of 64:
 //   warp 0        TMA: the tokens' activation tile [ntok x 64] fp16 (SWIZZLE_128B boxes of 64 rows) -> shared memory
-//   warps 2..17   decode: warp (h, s) streams strip s of the group with cp.async, decodes k-steps 4h..4h+3 of each unit
-//                 in registers (bit-exact fp16) and stores them as the UMMA A tile [128 x 64] (K-major, no swizzle) of
-//                 k-block 2 c + h
+//   warps 2..17   decode: warp (p, s) streams the chunks of parity p of strip s with cp.async, decodes each unit in
+//                 registers (bit-exact fp16) and stores it as two UMMA A tiles [128 x 64] (K-major, no swizzle):
+//                 k-blocks 2 c and 2 c + 1
 //   warp 1        one thread issues tcgen05.mma (M 128 = weight rows, N = tokens, K 16) into a [128 x 512] fp32
 //                 accumulator in TMEM; tcgen05.commit frees the stages.  Token tiles run 2..4 k-blocks ahead
 //                 (as many stages as fit 120 KB), weight tiles 4 stages (two per decode half)
@@ -33,7 +33,7 @@ constexpr int kPfTmemCols = 512;
 constexpr int kPfBoxRows = 64;                       // token rows per TMA box
 constexpr int kPfBoxBytes = kPfBoxRows * 128;        // [64 rows][64 k] fp16
 constexpr int kPfBBoxes = 15;                        // token-tile region: split into 2..4 stages of ceil(ntok / 64) boxes
-constexpr int kPfAStages = 4;                        // weight tiles: stages 0, 2 filled by decode half 0, stages 1, 3 by half 1
+constexpr int kPfAStages = 4;                        // weight tiles: stages 0, 1 filled by the even-chunk warps, 2, 3 by the odd-chunk warps
 constexpr int kPfABytes = 128 * 64 * 2;              // A tile of one k-block
 constexpr int kPfRingDepth = 2;
 constexpr int kPfDecodeWarps = 16;
@@ -131,39 +131,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// ---------------------------------------------------------------- decode warps: one half (4 k-steps) of each unit of a strip
+// ---------------------------------------------------------------- decode warps
 // A tile layout (K-major, no swizzle): 8 x 16-byte core matrices, 128 B apart along K, 1024 B apart along rows, i.e.
 // byte (row, k) = (row / 8) * 1024 + (k / 8) * 128 + (row % 8) * 16 + (k % 8) * 2.  A lane's fragment register of
-// k-step t, rows g + 8 (q & 1), k = 16 t + 2 t4 + 8 (q >> 1) lands at strip * 2048 + lane * 4 + constant.
-template <int HALF>
-struct ATileSink
-{
-    uint8_t* dst;   // A tile + strip * 2048 + lane * 4
-    template <int T>
-    __device__ __forceinline__ void operator()(std::integral_constant<int, T>, const uint32_t (&a)[4]) const
-    {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) *(uint32_t*)(dst + (q & 1) * 1024 + (2 * T + (q >> 1)) * 128) = a[q];
-    }
-};
-
-// k-steps 4 HALF .. 4 HALF + 3 of a unit whose words are in registers
-template <bool RES, int RC, int HALF, class Sink>
-__device__ __forceinline__ void decode_half(uint32_t* wb, uint32_t* wr, const UnitConsts& k, int lane, Sink&& sink)
-{
-    const int nxt = ring_next_lane(lane);
-    extend_stream<128>(wb, __shfl_sync(0xffffffffu, wb[0], nxt));
-    if constexpr (RES) extend_stream<Pattern<RC>::kBits>(wr, __shfl_sync(0xffffffffu, wr[0], nxt));
-    static_for<4>([&](auto tc) {
-        constexpr int T = decltype(tc)::value, TT = 4 * HALF + T;
-        uint32_t a[4];
-        a[0] = decode_pair<RES, RC, 4 * TT + 0>(wb, wr, k);
-        a[1] = decode_pair<RES, RC, 4 * TT + 1>(wb, wr, k);
-        a[2] = decode_pair<RES, RC, 4 * TT + 2>(wb, wr, k);
-        a[3] = decode_pair<RES, RC, 4 * TT + 3>(wb, wr, k);
-        sink(tc, a);
-    });
-}
+// k-step t (0..3 inside a 64-wide k-block), rows g + 8 (q & 1), k = 16 t + 2 t4 + 8 (q >> 1) lands at
+// strip * 2048 + lane * 4 + constant: conflict-free stores with no address arithmetic.
 
 struct PfShared
 {
@@ -174,11 +146,41 @@ struct PfShared
 // stages the token-tile region is cut into for a pass of nbox boxes per k-block
 __device__ __forceinline__ int b_stages(int nbox) { const int n = kPfBBoxes / nbox; return n > 4 ? 4 : n; }
 
-// one decode warp, one item: stream its strip over all chunks, fill the A tile of k-block 2 c + HALF for every chunk c.
-// `it` counts the k-blocks this warp has filled so far (phase of the stage barriers).  false = aborted.
-template <bool REFINED, int RC, int HALF>
-__device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int C, int NS, int nm, int lane, uint8_t* a_tiles,
-                                             uint8_t* ring, PfShared* sh, uint32_t& it)
+// A unit is decoded whole (8 k-steps) by one warp: k-steps 0..3 fill the A tile of k-block 2 c, k-steps 4..7 the
+// tile of k-block 2 c + 1.  The sink does the stage hand-over in between: wait until the MMAs that last read the
+// stage are done, store, make the stores visible to the tensor core, signal "full".
+struct UnitSink
+{
+    uint8_t* a_tiles; PfShared* sh; uint32_t it0; int strip_off; int lane; bool* ok;
+    template <int T>
+    __device__ __forceinline__ void operator()(std::integral_constant<int, T>, const uint32_t (&a)[4]) const
+    {
+        const uint32_t it = it0 + (T >> 2), sa = it % kPfAStages;
+        if constexpr ((T & 3) == 0)
+        {
+            if (*ok && !mbar_wait(&sh->empty_a[sa], ((it / kPfAStages) & 1u) ^ 1u, &sh->abort_flag)) *ok = false;
+            *ok = __shfl_sync(0xffffffffu, (int)*ok, 0) != 0;
+        }
+        if (*ok)
+        {
+            uint8_t* dst = a_tiles + sa * kPfABytes + strip_off + lane * 4;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) *(uint32_t*)(dst + (q & 1) * 1024 + (2 * (T & 3) + (q >> 1)) * 128) = a[q];
+            if constexpr ((T & 3) == 3)
+            {
+                fence_async_smem();                  // generic-proxy stores -> visible to the tensor core (async proxy)
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->full_a[sa]);
+            }
+        }
+    }
+};
+
+// One decode warp, one item: its strip over the chunks c = GROUP, GROUP + 2, ... (the other group of 8 warps takes the
+// other parity), i.e. k-blocks 4 i + 2 GROUP and + 1.  it_base = k-blocks of earlier items.  false = aborted.
+template <bool REFINED, int RC>
+__device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int C, int NS, int nm, int lane, int group,
+                                             uint8_t* a_tiles, uint8_t* ring, PfShared* sh, uint32_t it_base)
 {
     unsigned long long fl = ~0ull;
     if (REFINED && P.flags) fl = __ldg((const unsigned long long*)P.flags + strip);
@@ -187,14 +189,21 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
     auto res_unit = [&](int ch) -> size_t {
         return P.flags ? (size_t)strip * nm + __popcll(fl & ((1ull << ch) - 1ull)) : unit0 + ch;
     };
-    uint32_t var_lo = 0, var_hi = 0, dl_lo = 0, dl_hi = 0;      // per-unit scalars, one chunk per lane
+    // per-unit scalars of this warp's chunks, one chunk (group + 2 * lane) per lane: ring signs and, for refined units,
+    // the block word with its fp16 multiplier / addend (computed once here instead of by every lane of every unit)
+    uint32_t var_b = 0, ac = 0, mbn = 0;
     {
-        const int ca = lane, cb = 32 + lane;
-        if (P.var) { if (ca < C) var_lo = __ldg(P.var + unit0 + ca); if (cb < C) var_hi = __ldg(P.var + unit0 + cb); }
-        if constexpr (REFINED)
+        const int ch = group + 2 * lane;
+        if (ch < C)
         {
-            if (ca < C && ((fl >> ca) & 1ull)) dl_lo = __ldg(P.d4 + res_unit(ca));
-            if (cb < C && ((fl >> cb) & 1ull)) dl_hi = __ldg(P.d4 + res_unit(cb));
+            if (P.var) var_b = __ldg(P.var + unit0 + ch);
+            if constexpr (REFINED)
+                if ((fl >> ch) & 1ull)
+                {
+                    mbn = __ldg(P.d4 + res_unit(ch)) & 0xFFFFu;
+                    const UnitConsts k = consts_level4(mbn, 0u);
+                    ac = (k.a2 & 0xFFFFu) | (k.c2 << 16);
+                }
         }
     }
     auto issue = [&](int ch, uint8_t* st) {
@@ -205,62 +214,59 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
 #pragma unroll
     for (int d = 0; d < kPfRingDepth - 1; ++d)
     {
-        if (d < C) issue(d, ring + d * kStageBytes);
+        if (group + 2 * d < C) issue(group + 2 * d, ring + d * kStageBytes);
         cp_async_commit();
     }
-    int slot = 0, slot_in = kPfRingDepth - 1;
+    int slot = 0, slot_in = kPfRingDepth - 1, i = 0;
     bool ok = true;
-    for (int ch = 0; ch < C; ++ch)
+    for (int ch = group; ch < C; ch += 2, ++i)
     {
-        if (ch + kPfRingDepth - 1 < C) issue(ch + kPfRingDepth - 1, ring + slot_in * kStageBytes);
+        if (ch + 2 * (kPfRingDepth - 1) < C) issue(ch + 2 * (kPfRingDepth - 1), ring + slot_in * kStageBytes);
         cp_async_commit();
         cp_async_wait<kPfRingDepth - 1>();
         const uint8_t* st = ring + slot * kStageBytes;
         slot = slot + 1 == kPfRingDepth ? 0 : slot + 1;
         slot_in = slot_in + 1 == kPfRingDepth ? 0 : slot_in + 1;
-        const uint32_t vb = __shfl_sync(0xffffffffu, ch < 32 ? var_lo : var_hi, ch & 31);
+        const uint32_t vb = __shfl_sync(0xffffffffu, var_b, i);
         const uint32_t sign2 = ((vb >> (lane >> 2)) & 1u) * 0x80008000u;
         const uint4 b = *(const uint4*)(st + lane * 16);
         uint32_t wb[6] = {b.x, b.y, b.z, b.w, 0u, 0u};
-        // k-block `it` goes to stage it % 4 (always HALF or HALF + 2 for this warp); the MMAs that read that stage four
-        // k-blocks ago must have completed
-        const uint32_t sa = it % kPfAStages;
-        if (ok && !mbar_wait(&sh->empty_a[sa], ((it / kPfAStages) & 1u) ^ 1u, &sh->abort_flag)) ok = false;
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        const ATileSink<HALF> sink{a_tiles + sa * kPfABytes + strip % 8 * 2048 + lane * 4};
+        const UnitSink sink{a_tiles, sh, it_base + 2 * (uint32_t)ch, strip % 8 * 2048, lane, &ok};
         bool refined = false;
         if constexpr (REFINED) refined = (fl >> ch) & 1ull;
 #if NQ_PF_DEBUG == 1
-        if (ok) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->full_a[sa]); }
-        if (false)
-#else
         if (ok)
-#endif
-        {
-            if (refined)
+            for (int hh = 0; hh < 2; ++hh)
             {
-                const uint32_t dl = __shfl_sync(0xffffffffu, ch < 32 ? dl_lo : dl_hi, ch & 31);
-                uint32_t wr[Pattern<RC>::kWords + 2];
-                read_record<RC>(wr, st + 512, res_unit(ch) * 32 + lane, lane);
-                decode_half<true, RC, HALF>(wb, wr, consts_level4(dl, sign2), lane, sink);
+                const uint32_t it = it_base + 2 * ch + hh, sa = it % kPfAStages;
+                if (!mbar_wait(&sh->empty_a[sa], ((it / kPfAStages) & 1u) ^ 1u, &sh->abort_flag)) { ok = false; break; }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->full_a[sa]);
             }
-            else
-                decode_half<false, 0, HALF>(wb, nullptr, consts_level2(sign2), lane, sink);
-            fence_async_smem();                      // generic-proxy stores -> visible to the tensor core (async proxy)
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->full_a[sa]);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+#else
+        if (refined)
+        {
+            const uint32_t acw = __shfl_sync(0xffffffffu, ac, i), mb = __shfl_sync(0xffffffffu, mbn, i);
+            UnitConsts k;
+            k.a2 = __byte_perm(acw, 0u, 0x1010) ^ sign2; k.c2 = __byte_perm(acw, 0u, 0x3232) ^ sign2;
+            k.mrep = __byte_perm(mb, 0u, 0x0000); k.nrep = __byte_perm(mb, 0u, 0x1111);
+            uint32_t wr[Pattern<RC>::kWords + 2];
+            read_record<RC>(wr, st + 512, res_unit(ch) * 32 + lane, lane);
+            decode_words<true, RC>(wb, wr, k, lane, sink);
         }
-        it += 2;
+        else
+            decode_words<false, 0>(wb, nullptr, consts_level2(sign2), lane, sink);
+#endif
     }
     cp_async_wait<0>();
     return ok;
 }
 
-template <int HALF>
-__device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int rc, int strip, int C, int NS, int nm, int lane,
-                                            uint8_t* a_tiles, uint8_t* ring, PfShared* sh, uint32_t& it)
+__device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int rc, int strip, int C, int NS, int nm, int lane, int group,
+                                            uint8_t* a_tiles, uint8_t* ring, PfShared* sh, uint32_t it_base)
 {
-#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV, HALF>(P, strip, C, NS, nm, lane, a_tiles, ring, sh, it)
+#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV>(P, strip, C, NS, nm, lane, group, a_tiles, ring, sh, it_base)
     if (level < 4) NQ_RUN(false, 0);
     switch (rc)
     {
@@ -380,9 +386,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             const ProjPlanes P = planes_from_row(row, a.down);
             const int rc = (int)row[10 + a.down], nm = a.down ? a.nm_dn : a.nm_gu;
             uint8_t* ring = rings + dw * kPfRingDepth * kStageBytes;
-            uint32_t my_it = it + half;                 // this warp fills k-blocks 2 c + half
-            bool ok = half ? decode_item<1>(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, a_tiles, ring, sh, my_it)
-                           : decode_item<0>(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, a_tiles, ring, sh, my_it);
+            // group `half` of 8 warps decodes the chunks of that parity: k-blocks 4 i + 2 half and + 1
+            bool ok = decode_item(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, half, a_tiles, ring, sh, it);
             it += nkb;
             if (ok && lane == 0 && !mbar_wait(&sh->acc_full, nitem & 1u, &sh->abort_flag)) ok = false;
             ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
