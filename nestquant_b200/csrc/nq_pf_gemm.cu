@@ -32,7 +32,7 @@ constexpr int kPfTokens = 448;                       // tokens per pass (7 TMA b
 constexpr int kPfTmemCols = 512;
 constexpr int kPfBoxRows = 64;                       // token rows per TMA box
 constexpr int kPfBoxBytes = kPfBoxRows * 128;        // [64 rows][64 k] fp16
-constexpr int kPfBBoxes = 15;                        // token-tile region: split into 2..4 stages of ceil(ntok / 64) boxes
+constexpr int kPfBBoxes = 15;                        // token-tile region: 4 x 3, 3 x 5 or 2 x 7 boxes per stage
 constexpr int kPfAStages = 4;                        // weight tiles: stages 0, 1 filled by the even-chunk warps, 2, 3 by the odd-chunk warps
 constexpr int kPfABytes = 128 * 64 * 2;              // A tile of one k-block
 constexpr int kPfRingDepth = 2;
@@ -143,8 +143,12 @@ struct PfShared
     uint32_t tmem_base;
     volatile int abort_flag;
 };
-// stages the token-tile region is cut into for a pass of nbox boxes per k-block
-__device__ __forceinline__ int b_stages(int nbox) { const int n = kPfBBoxes / nbox; return n > 4 ? 4 : n; }
+// The token-tile region (15 boxes) is cut into stages of 3, 5 or 7 boxes (4, 3 or 2 stages) for a pass of nbox boxes
+// per k-block.  Passes with the same stage size share the stage barriers freely; when the stage size changes between
+// two items of a CTA the new stages overlap old ones at other indices, so the producer first waits until every stage
+// of the old layout has been released.
+__device__ __forceinline__ int b_stage_boxes(int nbox) { return nbox <= 3 ? 3 : nbox <= 5 ? 5 : 7; }
+__device__ __forceinline__ int b_stages(int nbox) { return nbox <= 3 ? 4 : nbox <= 5 ? 3 : 2; }
 
 // A unit is decoded whole (8 k-steps) by one warp: k-steps 0..3 fill the A tile of k-block 2 c, k-steps 4..7 the
 // tile of k-block 2 c + 1.  The sink does the stage hand-over in between: wait until the MMAs that last read the
@@ -319,12 +323,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
     const PfPass* passes = (const PfPass*)(a.plan + 4);
     uint32_t it = 0, nitem = 0;     // k-blocks / items handled so far by this role (phases of the A-stage and accumulator barriers)
     uint32_t used_b[4] = {0, 0, 0, 0};   // times each token-tile stage was used (its stage count changes from pass to pass)
+    int last_sbox = 0;                   // producer: stage size of the previous item
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, ++nitem)
     {
         const int pi = item / groups, wg = item - pi * groups;
         const PfPass ps = passes[pi];
         const int ntok16 = (ps.ntok + 15) & ~15, nbox = (ps.ntok + kPfBoxRows - 1) / kPfBoxRows, nb = b_stages(nbox);
+        const int sbox = b_stage_boxes(nbox);
         const int up = !a.down && wg >= a.I / 128;
         if (warp == 0)
         {
@@ -332,14 +338,18 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             if (lane == 0)
             {
                 const CUtensorMap* map = up ? &tmap1 : &tmap0;
-                for (int kb = 0; kb < nkb; ++kb)
+                bool ok = true;
+                if (sbox != last_sbox)
+                    for (int s = 0; ok && s < 4; ++s) ok = mbar_wait(&sh->empty_b[s], (used_b[s] & 1u) ^ 1u, &sh->abort_flag);
+                last_sbox = sbox;
+                for (int kb = 0; ok && kb < nkb; ++kb)
                 {
                     const int s = kb % nb;
                     if (!mbar_wait(&sh->empty_b[s], (used_b[s] & 1u) ^ 1u, &sh->abort_flag)) break;
                     ++used_b[s];
                     mbar_expect_tx(&sh->full_b[s], (uint32_t)nbox * kPfBoxBytes);
                     for (int j = 0; j < nbox; ++j)
-                        tma_load_2d(b_tiles + (s * nbox + j) * kPfBoxBytes, map, kb * 64, ps.row0 + j * kPfBoxRows, &sh->full_b[s]);
+                        tma_load_2d(b_tiles + (s * sbox + j) * kPfBoxBytes, map, kb * 64, ps.row0 + j * kPfBoxRows, &sh->full_b[s]);
                 }
             }
         }
@@ -357,7 +367,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
                         !mbar_wait(&sh->full_a[sa], (it / kPfAStages) & 1u, &sh->abort_flag)) { ok = false; break; }
                     ++used_b[s];
                     tc_fence_after();
-                    const uint32_t abase = saddr(a_tiles + sa * kPfABytes), bbase = saddr(b_tiles + s * nbox * kPfBoxBytes);
+                    const uint32_t abase = saddr(a_tiles + sa * kPfABytes), bbase = saddr(b_tiles + s * sbox * kPfBoxBytes);
                     // N <= 256 per instruction: one MMA per k-step, or two of (nearly) equal width
                     const int n0 = ntok16 <= 256 ? ntok16 : ((ntok16 / 2 + 15) & ~15);
 #if NQ_PF_DEBUG != 2

@@ -93,6 +93,29 @@ def test_prefill_matches_decode_path_and_oracle():
     assert rl2 <= 5e-4, rl2                       # same math, different fp32 accumulation order
 
 
+def test_prefill_glm_shape_fused_matches_library_gemm():
+    """Full-size expert shape (H 6144, I 2048, top-8), 32 experts, 1024 tokens: ~256 tokens per expert as in the
+    8192-token prefill of the 256-expert layer.  The fused GEMM must agree with the library GEMM on the decoded
+    weights, be deterministic, and scale linearly in the routing weights."""
+    from nestquant_b200 import synth
+    cfg = dict(synth.GLM); cfg["E"] = 32
+    levels = [4] * 24 + [2] * 6 + [0] * 2
+    L, _ = synth.build_layer(cfg, levels, seed=11, Bmax=1, masked={3, 17})
+    T = 1024
+    sel, rw = synth.routing(T, cfg["E"], cfg["topk"], 12)
+    x = synth.tokens(T, cfg["H"], 13).cuda()
+    sel, rw = sel.cuda(), rw.cuda()
+    y_lib = L.prefill(x, sel, rw, fused=False)
+    y = L.prefill(x, sel, rw)
+    y2 = L.prefill(x, sel, rw)
+    yh = L.prefill(x, sel, (rw.float() * 0.5).half())
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2)
+    ma, rl = layer_errors(y.cpu().numpy(), y_lib.cpu().numpy())
+    assert rl <= 1e-4 and ma <= MAX_ABS_TOL, (ma, rl)
+    assert layer_errors((2 * yh).cpu().numpy(), y.cpu().numpy())[1] <= 1e-3      # halving fp16 weights is exact up to subnormals
+
+
 def test_pf_helpers_reject_bad_sizes():
     from nestquant_b200 import ext
     from nestquant_b200.capi import NestQuantError
