@@ -12,7 +12,8 @@
 //   warp 1        one thread issues tcgen05.mma (M 128 = weight rows, N = tokens, K 16) into a [128 x 512] fp32
 //                 accumulator in TMEM; tcgen05.commit frees the stages.  Token tiles run 2..4 k-blocks ahead
 //                 (as many stages as fit 120 KB), weight tiles 4 stages (two per decode half)
-//   warps 2..17   epilogue: tcgen05.ld the accumulator and store fp32 rows acc[pair][128 columns] (coalesced)
+//   warps 2..17   epilogue: tcgen05.ld the accumulator and store fp32 rows acc[pair][128 columns] (coalesced); it runs
+//                 after the first unit of the CTA's next item has been decoded
 // Each decoded weight is used for every token of the pass, so decode cost is paid once per expert (for up to 448
 // tokens).  Tensor-pipe bound by intent; the decode instruction rate is the practical limit.
 // Every mbarrier wait is bounded: on time-out the CTA raises status[0], drains and returns.
@@ -182,9 +183,9 @@ struct UnitSink
 
 // One decode warp, one item: its strip over the chunks c = GROUP, GROUP + 2, ... (the other group of 8 warps takes the
 // other parity), i.e. k-blocks 4 i + 2 GROUP and + 1.  it_base = k-blocks of earlier items.  false = aborted.
-template <bool REFINED, int RC>
+template <bool REFINED, int RC, class Mid>
 __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int C, int NS, int nm, int lane, int group,
-                                             uint8_t* a_tiles, uint8_t* ring, PfShared* sh, uint32_t it_base)
+                                             uint8_t* a_tiles, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
 {
     unsigned long long fl = ~0ull;
     if (REFINED && P.flags) fl = __ldg((const unsigned long long*)P.flags + strip);
@@ -262,15 +263,17 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
         else
             decode_words<false, 0>(wb, nullptr, consts_level2(sign2), lane, sink);
 #endif
+        if (i == 0) mid();      // the previous item's epilogue, once this item's first tiles are on their way
     }
     cp_async_wait<0>();
     return ok;
 }
 
+template <class Mid>
 __device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int rc, int strip, int C, int NS, int nm, int lane, int group,
-                                            uint8_t* a_tiles, uint8_t* ring, PfShared* sh, uint32_t it_base)
+                                            uint8_t* a_tiles, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
 {
-#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV>(P, strip, C, NS, nm, lane, group, a_tiles, ring, sh, it_base)
+#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV>(P, strip, C, NS, nm, lane, group, a_tiles, ring, sh, it_base, mid)
     if (level < 4) NQ_RUN(false, 0);
     switch (rc)
     {
@@ -322,8 +325,36 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
     const int npass = a.plan[0], nitems = npass * groups;
     const PfPass* passes = (const PfPass*)(a.plan + 4);
     uint32_t it = 0, nitem = 0;     // k-blocks / items handled so far by this role (phases of the A-stage and accumulator barriers)
-    uint32_t used_b[4] = {0, 0, 0, 0};   // times each token-tile stage was used (its stage count changes from pass to pass)
+    uint32_t par_b = 0;                  // bit s: parity of the times token-tile stage s was used (its stage count changes from pass to pass)
     int last_sbox = 0;                   // producer: stage size of the previous item
+
+    // decode warps: accumulator [128 weight rows x ntok] of item number n of this CTA -> out.  TMEM lanes 32 q .. 32 q + 31
+    // (the quarter this warp may read) are weight rows; the four warps of a quarter take 32-column chunks in turn.
+    PfPass prev{};
+    int prev_wg = 0, prev_up = 0;
+    bool have_prev = false;
+    auto epilogue = [&](const PfPass& ps, int wg, int up, uint32_t n) {
+        bool ok = true;
+        if (lane == 0 && !mbar_wait(&sh->acc_full, n & 1u, &sh->abort_flag)) ok = false;
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) return;
+        tc_fence_after();
+        const int q = warp & 3, cpart = (warp - 2) >> 2;
+        const int ncol = (up ? wg - a.I / 128 : wg) * 128 + q * 32 + lane;
+        float* out = up ? a.out1 : a.out0;
+        const int ld = a.down ? a.H : a.I;
+        for (int c0 = cpart * 32; c0 < ps.ntok; c0 += 128)
+        {
+            uint32_t v[32];
+            tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c0, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (c0 + j < ps.ntok) out[(size_t)(ps.row0 + c0 + j) * ld + ncol] = __uint_as_float(v[j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->acc_empty);
+    };
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x, ++nitem)
     {
@@ -340,13 +371,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
                 const CUtensorMap* map = up ? &tmap1 : &tmap0;
                 bool ok = true;
                 if (sbox != last_sbox)
-                    for (int s = 0; ok && s < 4; ++s) ok = mbar_wait(&sh->empty_b[s], (used_b[s] & 1u) ^ 1u, &sh->abort_flag);
+                    for (int s = 0; ok && s < 4; ++s) ok = mbar_wait(&sh->empty_b[s], ((par_b >> s) & 1u) ^ 1u, &sh->abort_flag);
                 last_sbox = sbox;
                 for (int kb = 0; ok && kb < nkb; ++kb)
                 {
                     const int s = kb % nb;
-                    if (!mbar_wait(&sh->empty_b[s], (used_b[s] & 1u) ^ 1u, &sh->abort_flag)) break;
-                    ++used_b[s];
+                    if (!mbar_wait(&sh->empty_b[s], ((par_b >> s) & 1u) ^ 1u, &sh->abort_flag)) break;
+                    par_b ^= 1u << s;
                     mbar_expect_tx(&sh->full_b[s], (uint32_t)nbox * kPfBoxBytes);
                     for (int j = 0; j < nbox; ++j)
                         tma_load_2d(b_tiles + (s * sbox + j) * kPfBoxBytes, map, kb * 64, ps.row0 + j * kPfBoxRows, &sh->full_b[s]);
@@ -360,25 +391,30 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             {
                 bool ok = mbar_wait(&sh->acc_empty, (nitem & 1u) ^ 1u, &sh->abort_flag);   // epilogue of the previous item has drained TMEM
                 tc_fence_after();
+                // N <= 256 per instruction: one MMA per k-step, or two of (nearly) equal width.  The descriptors of a
+                // k-step differ from the stage's first one only in the start-address field (16-byte units), so each is
+                // formed by one 64-bit add and the issuing thread stays ahead of the tensor pipe.
+                const int n0 = ntok16 <= 256 ? ntok16 : ((ntok16 / 2 + 15) & ~15), n1 = ntok16 - n0;
+                const uint32_t idesc0 = instr_desc(n0), idesc1 = instr_desc(n1 > 0 ? n1 : 16);
+                const uint64_t adesc0 = smem_desc(saddr(a_tiles), 128, 1024, 0), bdesc0 = smem_desc(saddr(b_tiles), 16, 1024, 2);
                 for (int kb = 0; ok && kb < nkb; ++kb, ++it)
                 {
                     const int s = kb % nb, sa = it % kPfAStages;
-                    if (!mbar_wait(&sh->full_b[s], used_b[s] & 1u, &sh->abort_flag) ||
+                    if (!mbar_wait(&sh->full_b[s], (par_b >> s) & 1u, &sh->abort_flag) ||
                         !mbar_wait(&sh->full_a[sa], (it / kPfAStages) & 1u, &sh->abort_flag)) { ok = false; break; }
-                    ++used_b[s];
+                    par_b ^= 1u << s;
                     tc_fence_after();
-                    const uint32_t abase = saddr(a_tiles + sa * kPfABytes), bbase = saddr(b_tiles + s * sbox * kPfBoxBytes);
-                    // N <= 256 per instruction: one MMA per k-step, or two of (nearly) equal width
-                    const int n0 = ntok16 <= 256 ? ntok16 : ((ntok16 / 2 + 15) & ~15);
 #if NQ_PF_DEBUG != 2
-                    for (int c0 = 0; c0 < ntok16; c0 += n0)
+                    const uint64_t ad = adesc0 + (uint64_t)(sa * (kPfABytes >> 4)), bd = bdesc0 + (uint64_t)(s * sbox * (kPfBoxBytes >> 4));
+#pragma unroll
+                    for (int k16 = 0; k16 < 4; ++k16)
+                        tc_mma_f16(tmem, ad + k16 * 16, bd + k16 * 2, idesc0, (kb | k16) != 0);
+                    if (n1 > 0)
                     {
-                        const int n = ntok16 - c0 < n0 ? ntok16 - c0 : n0;
-                        const uint32_t idesc = instr_desc(n);
+                        const uint64_t bd1 = bd + (uint64_t)(n0 * 8);
 #pragma unroll
                         for (int k16 = 0; k16 < 4; ++k16)
-                            tc_mma_f16(tmem + c0, smem_desc(abase + k16 * 256, 128, 1024, 0),
-                                       smem_desc(bbase + c0 * 128 + k16 * 32, 16, 1024, 2), idesc, (kb | k16) != 0);
+                            tc_mma_f16(tmem + n0, ad + k16 * 16, bd1 + k16 * 2, idesc1, (kb | k16) != 0);
                     }
 #endif
                     tc_commit(&sh->empty_a[sa]);       // both arrive when the MMAs above have read their operands
@@ -396,34 +432,18 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             const ProjPlanes P = planes_from_row(row, a.down);
             const int rc = (int)row[10 + a.down], nm = a.down ? a.nm_dn : a.nm_gu;
             uint8_t* ring = rings + dw * kPfRingDepth * kStageBytes;
-            // group `half` of 8 warps decodes the chunks of that parity: k-blocks 4 i + 2 half and + 1
-            bool ok = decode_item(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, half, a_tiles, ring, sh, it);
+            // group `half` of 8 warps decodes the chunks of that parity: k-blocks 4 i + 2 half and + 1.  The epilogue
+            // of the previous item runs after this item's first unit is decoded: the MMAs of the previous item's last
+            // k-blocks finish meanwhile, and the tensor pipe finds tiles waiting when the accumulator is free again.
+            auto mid = [&]() { if (have_prev) { epilogue(prev, prev_wg, prev_up, nitem - 1); have_prev = false; } };
+            const bool ok = decode_item(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, half, a_tiles, ring, sh, it, mid);
             it += nkb;
-            if (ok && lane == 0 && !mbar_wait(&sh->acc_full, nitem & 1u, &sh->abort_flag)) ok = false;
-            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-            if (ok)
-            {
-                tc_fence_after();
-                // TMEM lanes 32 q .. 32 q + 31 (the quarter this warp may read) = weight rows; 128 token columns per warp
-                const int q = warp & 3, cpart = dw >> 2;
-                const int ncol = (up ? wg - a.I / 128 : wg) * 128 + q * 32 + lane;
-                float* out = up ? a.out1 : a.out0;
-                const int ld = a.down ? a.H : a.I;
-                for (int c0 = cpart * 128; c0 < cpart * 128 + 128 && c0 < ntok16; c0 += 32)
-                {
-                    uint32_t v[32];
-                    tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c0, v);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (c0 + j < ps.ntok) out[(size_t)(ps.row0 + c0 + j) * ld + ncol] = __uint_as_float(v[j]);
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sh->acc_empty);
-            }
+            mid();                                   // (an item of fewer than two chunks: its second warp group decodes nothing)
+            if (ok) { prev = ps; prev_wg = wg; prev_up = up; have_prev = true; }
         }
         if (sh->abort_flag) break;
     }
+    if (warp >= 2 && have_prev && !sh->abort_flag) epilogue(prev, prev_wg, prev_up, nitem - 1);
     if (sh->abort_flag && threadIdx.x == 0) atomicExch(a.status, 1);
     tc_fence_before();
     __syncthreads();
