@@ -179,6 +179,45 @@ def moe_bytes(H, I, level):
     return b + (3 * H + 3 * I) * 2
 
 
+def prefill_pieces(L, x, sel, rw):
+    """CUDA-event time (ms, median of 3) of each kernel of the fused prefill, called one by one as MoELayer.prefill does"""
+    import torch
+    from nestquant_b200 import ext as M
+    T, k = sel.shape
+    H, I, E, P, dev = L.H, L.I, L.E, T * k, x.device
+    i32, f16, f32 = torch.int32, torch.float16, torch.float32
+    flat = sel.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    pe, pt = flat[order].to(i32), (order // k).to(i32)
+    cnt = torch.zeros(E, dtype=i32, device=dev).scatter_add_(0, flat, torch.ones_like(flat, dtype=i32))
+    pos = torch.empty(P, dtype=i32, device=dev)
+    pos[order] = torch.arange(P, dtype=i32, device=dev)
+    plan = torch.empty(M.pf_plan_ints(E, P), dtype=i32, device=dev)
+    M.pf_plan(cnt, L.table, plan, P)
+    status = torch.zeros(1, dtype=i32, device=dev)
+    xg, xu = torch.empty(P, H, dtype=f16, device=dev), torch.empty(P, H, dtype=f16, device=dev)
+    zg, zd = torch.zeros(P, 4, dtype=f32, device=dev), torch.zeros(P, 4, dtype=f32, device=dev)
+    acc_g, acc_u = torch.empty(P, I, dtype=f32, device=dev), torch.empty(P, I, dtype=f32, device=dev)
+    hbuf, y = torch.empty(P, I, dtype=f16, device=dev), torch.empty(P, H, dtype=f32, device=dev)
+    out = torch.empty(T, H, dtype=f32, device=dev)
+    steps = [("pf_pre", lambda: M.pf_pre(x, pt, pe, L.table, xg, xu, zg, I)),
+             ("pf_gemm gate|up", lambda: M.pf_gemm(L.table, plan, xg, xu, acc_g, acc_u, H, I, L.nm_gu, L.nm_dn, False, status)),
+             ("pf_mid", lambda: M.pf_mid(acc_g, acc_u, zg, pe, L.table, hbuf, zd, H, I)),
+             ("pf_gemm down", lambda: M.pf_gemm(L.table, plan, hbuf, None, y, None, H, I, L.nm_gu, L.nm_dn, True, status)),
+             ("pf_combine", lambda: M.pf_combine(y, zd, pos, sel, rw, L.table, out, I))]
+    res = {}
+    for name, f in steps:
+        ts = []
+        for _ in range(4):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); f(); b.record(); torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        res[name] = sorted(ts[1:])[1]
+    if int(status.item()):
+        raise SystemExit("prefill: a device-side wait timed out inside the grouped GEMM")
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -321,6 +360,7 @@ def main():
     pf_ms = float(allmax(torch.tensor([a.elapsed_time(b) for a, b in pf], dtype=torch.float64, device=dev)).median())
     pf_flops = 2.0 * T_pf * topk * 3 * H * I
 
+    pieces = prefill_pieces(Lp, xp, selp, rwp) if world == 1 else None
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         tpeak = 1689.3
@@ -350,8 +390,9 @@ def main():
                 "decode_4tok": {"layer_us": r4["us_total"] / s4, "value": r4["bytes_total"] / r4["us_total"] / 1e3, "unit": UNIT,
                                 "bytes_per_step": r4["bytes_total"] / s4, "steps": s4},
                 "prefill": {"workload": "8192 tokens x top-8, all experts level 4", "ms": pf_ms, "tflops": pf_flops / pf_ms / 1e9,
-                            "frac_of_measured_tensor_peak": pf_flops / pf_ms / 1e9 / tpeak, "frac_of_nominal_2250": pf_flops / pf_ms / 1e9 / 2250.0,
-                            "parallelism": f"ep{world}" + (" all-to-all dispatch/combine" if world > 1 else "")},
+                            "frac_of_measured_tensor_peak": pf_flops / pf_ms / 1e9 / (tpeak * world), "frac_of_nominal_2250": pf_flops / pf_ms / 1e9 / (2250.0 * world),
+                            "parallelism": f"ep{world}" + (" all-to-all dispatch/combine" if world > 1 else ""),
+                            "kernels_ms": pieces},
                 "clocks": r1["clocks"]}
         # CPU baseline: the oracle port on one full step (rank 0, N = 1 only)
         if world == 1:
