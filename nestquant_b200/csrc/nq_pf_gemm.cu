@@ -25,7 +25,8 @@
 
 namespace nq {
 
-// timing experiments only: 1 = decode warps skip the decode, 2 = no MMAs are issued (results are then wrong)
+// timing experiments only (results are then wrong): 1 = decode warps skip the decode, 2 = no MMAs are issued, 3 = no
+// MMAs and no token-tile loads, 4 = as 1 with half of each token tile loaded, 5 = everything runs, half of each tile loaded
 #ifndef NQ_PF_DEBUG
 #define NQ_PF_DEBUG 0
 #endif
@@ -239,7 +240,7 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
         const UnitSink sink{a_tiles, sh, it_base + 2 * (uint32_t)ch, strip % 8 * 2048, lane, &ok};
         bool refined = false;
         if constexpr (REFINED) refined = (fl >> ch) & 1ull;
-#if NQ_PF_DEBUG == 1
+#if NQ_PF_DEBUG == 1 || NQ_PF_DEBUG == 4
         if (ok)
             for (int hh = 0; hh < 2; ++hh)
             {
@@ -378,9 +379,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
                     const int s = kb % nb;
                     if (!mbar_wait(&sh->empty_b[s], ((par_b >> s) & 1u) ^ 1u, &sh->abort_flag)) break;
                     par_b ^= 1u << s;
-                    mbar_expect_tx(&sh->full_b[s], (uint32_t)nbox * kPfBoxBytes);
-                    for (int j = 0; j < nbox; ++j)
+#if NQ_PF_DEBUG == 3
+                    mbar_arrive(&sh->full_b[s]);
+#else
+                    const int nld = NQ_PF_DEBUG >= 4 ? (nbox + 1) / 2 : nbox;
+                    mbar_expect_tx(&sh->full_b[s], (uint32_t)nld * kPfBoxBytes);
+                    for (int j = 0; j < nld; ++j)
                         tma_load_2d(b_tiles + (s * sbox + j) * kPfBoxBytes, map, kb * 64, ps.row0 + j * kPfBoxRows, &sh->full_b[s]);
+#endif
                 }
             }
         }
@@ -404,7 +410,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
                         !mbar_wait(&sh->full_a[sa], (it / kPfAStages) & 1u, &sh->abort_flag)) { ok = false; break; }
                     par_b ^= 1u << s;
                     tc_fence_after();
-#if NQ_PF_DEBUG != 2
+#if NQ_PF_DEBUG != 2 && NQ_PF_DEBUG != 3
                     const uint64_t ad = adesc0 + (uint64_t)(sa * (kPfABytes >> 4)), bd = bdesc0 + (uint64_t)(s * sbox * (kPfBoxBytes >> 4));
 #pragma unroll
                     for (int k16 = 0; k16 < 4; ++k16)
