@@ -30,6 +30,9 @@ namespace nq {
 #ifndef NQ_PF_DEBUG
 #define NQ_PF_DEBUG 0
 #endif
+#ifndef NQ_PF_SPLIT
+#define NQ_PF_SPLIT 256      // token tiles wider than this are multiplied as two column halves
+#endif
 constexpr int kPfTokens = 448;                       // tokens per pass (7 TMA boxes; the accumulator has 512 TMEM columns)
 constexpr int kPfTmemCols = 512;
 constexpr int kPfBoxRows = 64;                       // token rows per TMA box
@@ -91,6 +94,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     *abort_flag = 1;
     return false;
 }
+// The producer and MMA warps run their loops with all 32 lanes converged (so that addresses, descriptors and
+// coordinates are warp-uniform values) and one elected lane issues the asynchronous instruction.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
+{
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
+}
+__device__ __forceinline__ void mbar_expect_tx_elect(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                 "@e mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(saddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_elect(uint64_t* bar)
+{
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t@e mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_elect(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                 "@e cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}"
+                 ::"r"(saddr(dst)), "l"(map), "r"(saddr(bar)), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -99,6 +123,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit_elect(uint64_t* bar)
+{
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                 "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(saddr(bar)) : "memory");
+}
 __device__ __forceinline__ void tc_commit(uint64_t* bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
@@ -108,6 +137,56 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint
 {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The four K = 16 steps of one 64-wide k-block, issued by one elected lane of a converged warp: A and B descriptors advance by 256 B and 32 B (16-byte units, low word
+// only: shared-memory addresses fit its 14-bit field).  first == 0: the very first MMA overwrites the accumulator.
+__device__ __forceinline__ void tc_mma_kblock(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                              uint32_t first)
+{
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\t.reg .b32 ta, tb;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "setp.eq.b32 p, %5, %5;\n\t"
+        "add.u32 ta, %1, 16;\n\tadd.u32 tb, %3, 2;\n\tmov.b64 da, {ta, %2};\n\tmov.b64 db, {tb, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "add.u32 ta, %1, 32;\n\tadd.u32 tb, %3, 4;\n\tmov.b64 da, {ta, %2};\n\tmov.b64 db, {tb, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "add.u32 ta, %1, 48;\n\tadd.u32 tb, %3, 6;\n\tmov.b64 da, {ta, %2};\n\tmov.b64 db, {tb, %4};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(first) : "memory");
+}
+// The same for a token tile cut into two column halves with their own accumulator columns: the two accumulation
+// chains alternate, so that an MMA never follows directly on the one it depends on.
+__device__ __forceinline__ void tc_mma_kblock2(uint32_t tmem_d0, uint32_t tmem_d1, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo0, uint32_t b_lo1,
+                                               uint32_t b_hi, uint32_t idesc0, uint32_t idesc1, uint32_t first)
+{
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\t.reg .b32 ta, tb;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %9, 0;\n\t"
+        "mov.b64 da, {%2, %3};\n\tmov.b64 db, {%4, %6};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+        "mov.b64 db, {%5, %6};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %8, p;\n\t"
+        "setp.eq.b32 p, %7, %7;\n\t"
+        "add.u32 ta, %2, 16;\n\tadd.u32 tb, %4, 2;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %6};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+        "add.u32 tb, %5, 2;\n\tmov.b64 db, {tb, %6};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %8, p;\n\t"
+        "add.u32 ta, %2, 32;\n\tadd.u32 tb, %4, 4;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %6};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+        "add.u32 tb, %5, 4;\n\tmov.b64 db, {tb, %6};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %8, p;\n\t"
+        "add.u32 ta, %2, 48;\n\tadd.u32 tb, %4, 6;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %6};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
+        "add.u32 tb, %5, 6;\n\tmov.b64 db, {tb, %6};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %8, p;\n\t"
+        "}"
+        ::"r"(tmem_d0), "r"(tmem_d1), "r"(a_lo), "r"(a_hi), "r"(b_lo0), "r"(b_lo1), "r"(b_hi), "r"(idesc0), "r"(idesc1), "r"(first) : "memory");
 }
 // shared-memory operand descriptor: start address, leading / stride byte offsets (all >> 4), descriptor version 1,
 // layout 0 = no swizzle, 2 = 128-byte swizzle
@@ -367,67 +446,54 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
         if (warp == 0)
         {
             // ---- token tiles by TMA, up to nb k-blocks ahead of the MMAs
-            if (lane == 0)
+            const CUtensorMap* map = up ? &tmap1 : &tmap0;
+            bool ok = true;
+            if (sbox != last_sbox)
+                for (int s = 0; ok && s < 4; ++s) ok = mbar_wait_warp(&sh->empty_b[s], ((par_b >> s) & 1u) ^ 1u, &sh->abort_flag);
+            last_sbox = sbox;
+            for (int kb = 0, s = 0; ok && kb < nkb; ++kb, s = s + 1 == nb ? 0 : s + 1)
             {
-                const CUtensorMap* map = up ? &tmap1 : &tmap0;
-                bool ok = true;
-                if (sbox != last_sbox)
-                    for (int s = 0; ok && s < 4; ++s) ok = mbar_wait(&sh->empty_b[s], ((par_b >> s) & 1u) ^ 1u, &sh->abort_flag);
-                last_sbox = sbox;
-                for (int kb = 0; ok && kb < nkb; ++kb)
-                {
-                    const int s = kb % nb;
-                    if (!mbar_wait(&sh->empty_b[s], ((par_b >> s) & 1u) ^ 1u, &sh->abort_flag)) break;
-                    par_b ^= 1u << s;
+                if (!mbar_wait_warp(&sh->empty_b[s], ((par_b >> s) & 1u) ^ 1u, &sh->abort_flag)) break;
+                par_b ^= 1u << s;
 #if NQ_PF_DEBUG == 3
-                    mbar_arrive(&sh->full_b[s]);
+                mbar_arrive_elect(&sh->full_b[s]);
 #else
-                    const int nld = NQ_PF_DEBUG >= 4 ? (nbox + 1) / 2 : nbox;
-                    mbar_expect_tx(&sh->full_b[s], (uint32_t)nld * kPfBoxBytes);
-                    for (int j = 0; j < nld; ++j)
-                        tma_load_2d(b_tiles + (s * sbox + j) * kPfBoxBytes, map, kb * 64, ps.row0 + j * kPfBoxRows, &sh->full_b[s]);
+                const int nld = NQ_PF_DEBUG >= 4 ? (nbox + 1) / 2 : nbox;
+                mbar_expect_tx_elect(&sh->full_b[s], (uint32_t)nld * kPfBoxBytes);
+                for (int j = 0; j < nld; ++j)
+                    tma_load_2d_elect(b_tiles + (s * sbox + j) * kPfBoxBytes, map, kb * 64, ps.row0 + j * kPfBoxRows, &sh->full_b[s]);
 #endif
-                }
             }
         }
         else if (warp == 1)
         {
             // ---- MMA issue
-            if (lane == 0)
+            bool ok = mbar_wait_warp(&sh->acc_empty, (nitem & 1u) ^ 1u, &sh->abort_flag);   // epilogue of the previous item has drained TMEM
+            tc_fence_after();
+            // N <= 256 per instruction: one MMA per k-step, or two of (nearly) equal width
+            const int n0 = ntok16 <= NQ_PF_SPLIT ? ntok16 : ((ntok16 / 2 + 15) & ~15), n1 = ntok16 - n0;
+            const uint32_t idesc0 = instr_desc(n0), idesc1 = instr_desc(n1 > 0 ? n1 : 16);
+            const uint64_t adesc0 = smem_desc(saddr(a_tiles), 128, 1024, 0), bdesc0 = smem_desc(saddr(b_tiles), 16, 1024, 2);
+            const uint32_t a_lo0 = (uint32_t)adesc0, a_hi = (uint32_t)(adesc0 >> 32), b_lo0 = (uint32_t)bdesc0, b_hi = (uint32_t)(bdesc0 >> 32);
+            const uint32_t b_step = (uint32_t)(sbox * (kPfBoxBytes >> 4));
+            uint32_t s = 0, b_lo = b_lo0;                 // token-tile stage of this k-block and its descriptor
+            for (int kb = 0; ok && kb < nkb; ++kb, ++it)
             {
-                bool ok = mbar_wait(&sh->acc_empty, (nitem & 1u) ^ 1u, &sh->abort_flag);   // epilogue of the previous item has drained TMEM
+                const uint32_t sa = it % kPfAStages;
+                if (!mbar_wait_warp(&sh->full_b[s], (par_b >> s) & 1u, &sh->abort_flag) ||
+                    !mbar_wait_warp(&sh->full_a[sa], (it / kPfAStages) & 1u, &sh->abort_flag)) { ok = false; break; }
+                par_b ^= 1u << s;
                 tc_fence_after();
-                // N <= 256 per instruction: one MMA per k-step, or two of (nearly) equal width.  The descriptors of a
-                // k-step differ from the stage's first one only in the start-address field (16-byte units), so each is
-                // formed by one 64-bit add and the issuing thread stays ahead of the tensor pipe.
-                const int n0 = ntok16 <= 256 ? ntok16 : ((ntok16 / 2 + 15) & ~15), n1 = ntok16 - n0;
-                const uint32_t idesc0 = instr_desc(n0), idesc1 = instr_desc(n1 > 0 ? n1 : 16);
-                const uint64_t adesc0 = smem_desc(saddr(a_tiles), 128, 1024, 0), bdesc0 = smem_desc(saddr(b_tiles), 16, 1024, 2);
-                for (int kb = 0; ok && kb < nkb; ++kb, ++it)
-                {
-                    const int s = kb % nb, sa = it % kPfAStages;
-                    if (!mbar_wait(&sh->full_b[s], (par_b >> s) & 1u, &sh->abort_flag) ||
-                        !mbar_wait(&sh->full_a[sa], (it / kPfAStages) & 1u, &sh->abort_flag)) { ok = false; break; }
-                    par_b ^= 1u << s;
-                    tc_fence_after();
 #if NQ_PF_DEBUG != 2 && NQ_PF_DEBUG != 3
-                    const uint64_t ad = adesc0 + (uint64_t)(sa * (kPfABytes >> 4)), bd = bdesc0 + (uint64_t)(s * sbox * (kPfBoxBytes >> 4));
-#pragma unroll
-                    for (int k16 = 0; k16 < 4; ++k16)
-                        tc_mma_f16(tmem, ad + k16 * 16, bd + k16 * 2, idesc0, (kb | k16) != 0);
-                    if (n1 > 0)
-                    {
-                        const uint64_t bd1 = bd + (uint64_t)(n0 * 8);
-#pragma unroll
-                        for (int k16 = 0; k16 < 4; ++k16)
-                            tc_mma_f16(tmem + n0, ad + k16 * 16, bd1 + k16 * 2, idesc1, (kb | k16) != 0);
-                    }
+                const uint32_t a_lo = a_lo0 + sa * (kPfABytes >> 4);
+                if (n1 > 0) tc_mma_kblock2(tmem, tmem + n0, a_lo, a_hi, b_lo, b_lo + (uint32_t)(n0 * 8), b_hi, idesc0, idesc1, (uint32_t)kb);
+                else tc_mma_kblock(tmem, a_lo, a_hi, b_lo, b_hi, idesc0, (uint32_t)kb);
 #endif
-                    tc_commit(&sh->empty_a[sa]);       // both arrive when the MMAs above have read their operands
-                    tc_commit(&sh->empty_b[s]);
-                }
-                if (ok) tc_commit(&sh->acc_full);
+                tc_commit_elect(&sh->empty_a[sa]);       // both arrive when the MMAs above have read their operands
+                tc_commit_elect(&sh->empty_b[s]);
+                if (++s == (uint32_t)nb) { s = 0; b_lo = b_lo0; } else b_lo += b_step;
             }
+            if (ok) tc_commit_elect(&sh->acc_full);
         }
         else
         {
