@@ -5,11 +5,15 @@
 //   pf_combine  out[token]  = sum over the token's picks in pick order     (no atomics: bitwise repeatable)
 //   pf_hits     routing-hit export
 // Replaces nq_pf_pre / nq_pf_mid / nq_pf_post / nq_pf_hits of the reference (sm120/nqmoe.cu:1081-1245,1258-1293).
-// All of them are HBM-bound elementwise passes over [pairs][H] or [pairs][I] arrays; a warp owns a 128-wide group
-// (one Hadamard block), a CTA owns a pair.
+// All of them are HBM-bound elementwise passes over [pairs][H] or [pairs][I] arrays; a CTA owns a pair (or a token), a
+// warp eight 128-wide groups (Hadamard blocks) at a time, 32 consecutive columns per lane.
 #include "nq_common.cuh"
 #include "nq_format.cuh"
 #include "nq_rotate.cuh"
+
+#ifndef NQ_PF_EW_BLOCKS
+#define NQ_PF_EW_BLOCKS 3     // resident 256-thread CTAs the elementwise passes are compiled for (register cap)
+#endif
 
 namespace nq {
 
@@ -34,52 +38,68 @@ __device__ __forceinline__ float warp_sum(float d)
     return d;
 }
 
-// one CTA (256 threads) per pair
-__global__ void __launch_bounds__(256) pf_pre_kernel(const __half* __restrict__ x, const int* __restrict__ pt, const int* __restrict__ pe,
+// Thread layout of the passes below: a warp task = 8 consecutive 128-wide groups (1024 columns) of one row; lanes
+// 4 v .. 4 v + 3 hold group v, 32 columns each (wht128_x8 and its maps).  Groups past the end of the row are idle lanes.
+__device__ __forceinline__ float quad_sum(float d)
+{
+    d += __shfl_xor_sync(0xffffffffu, d, 1);
+    return d + __shfl_xor_sync(0xffffffffu, d, 2);
+}
+// one CTA per pair, one warp per 1024 columns
+__global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(const __half* __restrict__ x, const int* __restrict__ pt, const int* __restrict__ pe,
                                                      const int64_t* __restrict__ table, __half* xg, __half* xu, float* zg, int H, int I)
 {
-    const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int64_t* row = table + (int64_t)pe[p] * kTableWidth;
     const int level = (int)row[0];
     if (level <= 0) return;
     const __half* scales = (const __half*)row[9];
+    const __half* su_u = scales + 2 * H + 3 * I;
     const __half* xr = x + (size_t)pt[p] * H;
     const int ng = H / 128;
-    for (int task = warp; task < 2 * ng; task += 8)
+    for (int g0 = warp * 8; g0 < ng; g0 += nwarp * 8)
     {
-        const int up = task >= ng, k = (task - up * ng) * 128 + lane * 4;
-        const __half* su = up ? scales + 2 * H + 3 * I : scales;
-        float f[4], s[4];
-        load4h(xr + k, f); load4h(su + k, s);
-        float v[4] = {f[0] * s[0], f[1] * s[1], f[2] * s[2], f[3] * s[3]};
-        wht128(v, lane);
-        store4h((up ? xu : xg) + (size_t)p * H + k, v);
+        const int grp = g0 + (lane >> 2), k = grp * 128, q = lane & 3;
+        const bool live = grp < ng;
+        uint32_t xw[16];
+        float v[32];
+        if (live) load16w_mapH(xr + k, q, xw);
+#pragma unroll
+        for (int up = 0; up < 2; ++up)
+        {
+            if (live) mul32h_mapH(xw, (up ? su_u : scales) + k, q, v);
+            else
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            wht128_x8(v, lane);
+            if (live) store32h_mapH((up ? xu : xg) + (size_t)p * H + k, q, v);
+        }
     }
     const LowRank L = low_rank_of(row, level);
-    if (warp < 4)
+    for (int r = warp; r < 4; r += nwarp)
     {
         float d = 0.f;
-        if (warp < L.rg)
+        if (r < L.rg)
         {
             for (int k = lane * 4; k < H; k += 128)
             {
                 float f[4], v[4];
-                load4h(xr + k, f); load4h(L.lr + (size_t)warp * H + k, v);
+                load4h(xr + k, f); load4h(L.lr + (size_t)r * H + k, v);
                 d += f[0] * v[0] + f[1] * v[1] + f[2] * v[2] + f[3] * v[3];
             }
             d = warp_sum(d);
         }
-        if (lane == 0) zg[(size_t)p * 4 + warp] = d;
+        if (lane == 0) zg[(size_t)p * 4 + r] = d;
     }
 }
 
-// one CTA (128 threads) per pair; dynamic shared memory: I floats (staging for the 512-wide rotation)
-__global__ void __launch_bounds__(128) pf_mid_kernel(const float* __restrict__ acc_g, const float* __restrict__ acc_u, const float* __restrict__ zg,
+// one CTA per pair, one warp per 1024 columns; dynamic shared memory: I floats (staging for the 512-wide rotation)
+__global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_mid_kernel(const float* __restrict__ acc_g, const float* __restrict__ acc_u, const float* __restrict__ zg,
                                                      const int* __restrict__ pe, const int64_t* __restrict__ table, __half* h, float* zd, int H, int I)
 {
     extern __shared__ float stage[];
     __shared__ float zpart[64][4];
-    const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, ng = I / 128;
+    const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5, ng = I / 128;
     const int64_t* row = table + (int64_t)pe[p] * kTableWidth;
     const int level = (int)row[0];
     if (level <= 0) return;
@@ -90,47 +110,49 @@ __global__ void __launch_bounds__(128) pf_mid_kernel(const float* __restrict__ a
     float z[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) z[r] = zg[(size_t)p * 4 + r];
-    for (int grp = warp; grp < ng; grp += 4)
+    for (int g0 = warp * 8; g0 < ng; g0 += nwarp * 8)
     {
-        const int col = grp * 128 + lane * 4;
-        float gu[2][4];
+        const int grp = g0 + (lane >> 2), col = grp * 128, q = lane & 3;
+        const bool live = grp < ng;
+        float g[32], v[32];
 #pragma unroll
         for (int up = 0; up < 2; ++up)
         {
-            const float4 f = *(const float4*)((up ? acc_u : acc_g) + (size_t)p * I + col);
-            float v[4] = {f.x, f.y, f.z, f.w}, s[4];
-            wht128(v, lane);
-            load4h((up ? sv_u : sv_g) + col, s);
+            if (live) load32f_mapF((up ? acc_u : acc_g) + (size_t)p * I + col, q, v);
+            else
 #pragma unroll
-            for (int i = 0; i < 4; ++i) v[i] *= s[i];
-            for (int r = 0; r < L.rg; ++r)
+                for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            wht128_x8(v, lane);
+            if (live)
             {
-                float u2[4], u4[4] = {0.f, 0.f, 0.f, 0.f};
-                const size_t o = (size_t)(up * L.rg + r) * I + col;
-                load4h(L.lr + (size_t)L.rg * H + o, u2);
-                if (L.lr4) load4h(L.lr4 + o, u4);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) v[i] += z[r] * u2[i] + z[r] * u4[i];
+                scale32h_mapF((up ? sv_u : sv_g) + col, q, v);
+                for (int r = 0; r < L.rg; ++r)
+                {
+                    const size_t o = (size_t)(up * L.rg + r) * I + col;
+                    axpy32h_mapF(L.lr + (size_t)L.rg * H + o, q, z[r], v);
+                    if (L.lr4) axpy32h_mapF(L.lr4 + o, q, z[r], v);
+                }
             }
+            if (up == 0)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) gu[up][i] = v[i];
+                for (int i = 0; i < 32; ++i) g[i] = v[i];
         }
-        float v[4], s[4];
-        load4h(su_d + col, s);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = silu(gu[0][i]) * gu[1][i];
+        for (int i = 0; i < 32; ++i) v[i] = live ? silu(g[i]) * v[i] : 0.f;
         for (int r = 0; r < L.rd; ++r)
         {
-            float vd[4];
-            load4h(L.lr + (size_t)L.rg * H + 2 * (size_t)L.rg * I + (size_t)r * I + col, vd);
-            const float d = warp_sum(v[0] * vd[0] + v[1] * vd[1] + v[2] * vd[2] + v[3] * vd[3]);
-            if (lane == 0) zpart[grp][r] = d;
+            float d = 0.f;
+            if (live) d = dot32h_mapF(L.lr + (size_t)L.rg * H + 2 * (size_t)L.rg * I + (size_t)r * I + col, q, v);
+            d = quad_sum(d);
+            if (live && (lane & 3) == 0) zpart[grp][r] = d;
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] *= s[i];
-        wht128(v, lane);
-        if (hw <= 128) store4h(h + (size_t)p * I + col, v);
-        else *(float4*)(stage + col) = make_float4(v[0], v[1], v[2], v[3]);
+        if (live) scale32h_mapF(su_d + col, q, v);
+        wht128_x8(v, lane);
+        if (live)
+        {
+            if (hw <= 128) store32h_mapF(h + (size_t)p * I + col, q, v);
+            else store32f_mapF(stage + col, q, v);
+        }
     }
     __syncthreads();
     if (threadIdx.x < 4)      // column groups added in order: the same sum whatever the launch shape
@@ -144,7 +166,7 @@ __global__ void __launch_bounds__(128) pf_mid_kernel(const float* __restrict__ a
     {
         const int nb = hw / 128;
         const float rs = rsqrtf((float)nb);
-        for (int blk = warp; blk < ng; blk += 4)
+        for (int blk = warp; blk < ng; blk += nwarp)
         {
             const int b0 = blk / nb * nb, ob = blk - b0;
             float o[4] = {0.f, 0.f, 0.f, 0.f};
@@ -161,77 +183,85 @@ __global__ void __launch_bounds__(128) pf_mid_kernel(const float* __restrict__ a
     }
 }
 
-// rw * (WHT128(y) * sv_o + z_dn (U2_d [+ U4_d])) for output columns [col, col + 4) of pair p; false if the pair adds nothing
+// v = rw * (WHT128(y) * sv_o + z_dn (U2_d [+ U4_d])) for the lane's 32 output columns of the group at col of pair p (live lanes
+// only load and scale; every lane takes part in the rotation); false if the pair adds nothing (warp-uniform)
 __device__ __forceinline__ bool pair_output(const float* __restrict__ y, const float* __restrict__ zd, int p, int e, float w,
-                                            const int64_t* __restrict__ table, int H, int I, int col, int lane, float (&v)[4])
+                                            const int64_t* __restrict__ table, int H, int I, int col, bool live, int lane, float (&v)[32])
+// (col = first column of the lane's group, columns by map F)
 {
     const int64_t* row = table + (int64_t)e * kTableWidth;
     const int level = (int)row[0];
     if (level <= 0 || w == 0.f) return false;
     const __half* sv_o = (const __half*)row[9] + H + 3 * I;
     const LowRank L = low_rank_of(row, level);
-    const float4 f = *(const float4*)(y + (size_t)p * H + col);
-    float s[4];
-    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
-    wht128(v, lane);
-    load4h(sv_o + col, s);
+    const int q = lane & 3;
+    if (live) load32f_mapF(y + (size_t)p * H + col, q, v);
+    else
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] *= s[i];
-    const size_t ou = (size_t)L.rg * H + 2 * (size_t)L.rg * I + (size_t)L.rd * I;
-    for (int r = 0; r < L.rd; ++r)
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+    wht128_x8(v, lane);
+    if (live)
     {
-        const float z = zd[(size_t)p * 4 + r];
-        float u2[4], u4[4] = {0.f, 0.f, 0.f, 0.f};
-        load4h(L.lr + ou + (size_t)r * H + col, u2);
-        if (L.lr4) load4h(L.lr4 + 2 * (size_t)L.rg * I + (size_t)r * H + col, u4);
+        scale32h_mapF(sv_o + col, q, v);
+        const size_t ou = (size_t)L.rg * H + 2 * (size_t)L.rg * I + (size_t)L.rd * I;
+        for (int r = 0; r < L.rd; ++r)
+        {
+            const float z = zd[(size_t)p * 4 + r];
+            axpy32h_mapF(L.lr + ou + (size_t)r * H + col, q, z, v);
+            if (L.lr4) axpy32h_mapF(L.lr4 + 2 * (size_t)L.rg * I + (size_t)r * H + col, q, z, v);
+        }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] += z * u2[i] + z * u4[i];
+        for (int i = 0; i < 32; ++i) v[i] *= w;
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] *= w;
     return true;
 }
 
-// one CTA (256 threads) per pair: atomic accumulation into out[token]
-__global__ void __launch_bounds__(256) pf_post_kernel(const float* __restrict__ y, const float* __restrict__ zd, const int* __restrict__ pt,
+// one CTA per pair: atomic accumulation into out[token]
+__global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_post_kernel(const float* __restrict__ y, const float* __restrict__ zd, const int* __restrict__ pt,
                                                       const int* __restrict__ pe, const __half* __restrict__ prw,
                                                       const int64_t* __restrict__ table, float* out, int H, int I)
 {
-    const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5, ng = H / 128;
     const float w = __half2float(prw[p]);
     float* op = out + (size_t)pt[p] * H;
-    for (int grp = warp; grp < H / 128; grp += 8)
+    for (int g0 = warp * 8; g0 < ng; g0 += nwarp * 8)
     {
-        float v[4];
-        const int col = grp * 128 + lane * 4;
-        if (!pair_output(y, zd, p, pe[p], w, table, H, I, col, lane, v)) return;   // CTA-uniform
+        float v[32];
+        const int grp = g0 + (lane >> 2), col = grp * 128;
+        const bool live = grp < ng;
+        if (!pair_output(y, zd, p, pe[p], w, table, H, I, col, live, lane, v)) return;   // CTA-uniform
+        if (live)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) atomicAdd(op + col + i, v[i]);
+            for (int i = 0; i < 32; ++i) atomicAdd(op + col + 16 * (i >> 2) + 4 * (lane & 3) + (i & 3), v[i]);
     }
 }
 
-// one CTA (256 threads) per token: picks added in pick order, out written once.  pos[t * topk + k] = index of that pick
-// in the expert-sorted pair arrays.
-__global__ void __launch_bounds__(256) pf_combine_kernel(const float* __restrict__ y, const float* __restrict__ zd, const int* __restrict__ pos,
+// one CTA per token: picks added in pick order, out written once.  pos[t * topk + k] = index of that pick in the
+// expert-sorted pair arrays.
+__global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_combine_kernel(const float* __restrict__ y, const float* __restrict__ zd, const int* __restrict__ pos,
                                                          const int64_t* __restrict__ sel, const __half* __restrict__ rw,
                                                          const int64_t* __restrict__ table, float* out, int topk, int E, int H, int I)
 {
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int grp = warp; grp < H / 128; grp += 8)
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5, ng = H / 128;
+    for (int g0 = warp * 8; g0 < ng; g0 += nwarp * 8)
     {
-        const int col = grp * 128 + lane * 4;
-        float o[4] = {0.f, 0.f, 0.f, 0.f};
+        const int grp = g0 + (lane >> 2), col = grp * 128;
+        const bool live = grp < ng;
+        float o[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0.f;
         for (int k = 0; k < topk; ++k)
         {
             const int64_t e = sel[(size_t)t * topk + k];
             if (e < 0 || e >= E) continue;
-            float v[4];
-            if (!pair_output(y, zd, pos[(size_t)t * topk + k], (int)e, __half2float(rw[(size_t)t * topk + k]), table, H, I, col, lane, v))
+            float v[32];
+            if (!pair_output(y, zd, pos[(size_t)t * topk + k], (int)e, __half2float(rw[(size_t)t * topk + k]), table, H, I, col, live, lane, v))
                 continue;
+            if (live)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) o[i] += v[i];
+                for (int i = 0; i < 32; ++i) o[i] += v[i];
         }
-        *(float4*)(out + (size_t)t * H + col) = make_float4(o[0], o[1], o[2], o[3]);
+        if (live) store32f_mapF(out + (size_t)t * H + col, lane & 3, o);
     }
 }
 
@@ -240,6 +270,9 @@ __global__ void pf_hits_kernel(const int* __restrict__ counts, int* hits, int E)
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e < E && counts[e]) atomicAdd(hits + e, counts[e]);
 }
+
+// threads per CTA of the passes above: one warp per 1024 columns of the row, at most 8 warps
+static int pf_threads(int cols) { const int w = (cols + 1023) / 1024; return 32 * (w > 8 ? 8 : w); }
 
 }  // namespace nq
 
@@ -255,7 +288,7 @@ int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const 
     NQ_REQUIRE(x && pt && pe && table && xg && xu && zg, "nq_pf_pre: null pointer");
     NQ_SHAPE_OK("nq_pf_pre");
     NQ_REQUIRE(nq::aligned16(x) && nq::aligned16(xg) && nq::aligned16(xu), "nq_pf_pre: x, xg, xu must be 16-byte aligned");
-    nq::pf_pre_kernel<<<R, 256, 0, (cudaStream_t)stream>>>((const __half*)x, pt, pe, table, (__half*)xg, (__half*)xu, zg, H, I);
+    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>((const __half*)x, pt, pe, table, (__half*)xg, (__half*)xu, zg, H, I);
     return nq::check_launch("nq_pf_pre");
 }
 
@@ -267,7 +300,7 @@ int nq_pf_mid(const float* acc_g, const float* acc_u, const float* zg, const int
     NQ_REQUIRE(acc_g && acc_u && zg && pe && table && h && zd, "nq_pf_mid: null pointer");
     NQ_SHAPE_OK("nq_pf_mid");
     NQ_REQUIRE(nq::aligned16(acc_g) && nq::aligned16(acc_u) && nq::aligned16(h), "nq_pf_mid: acc_g, acc_u, h must be 16-byte aligned");
-    nq::pf_mid_kernel<<<R, 128, (size_t)I * 4, (cudaStream_t)stream>>>(acc_g, acc_u, zg, pe, table, (__half*)h, zd, H, I);
+    nq::pf_mid_kernel<<<R, nq::pf_threads(I), (size_t)I * 4, (cudaStream_t)stream>>>(acc_g, acc_u, zg, pe, table, (__half*)h, zd, H, I);
     return nq::check_launch("nq_pf_mid");
 }
 
@@ -279,7 +312,7 @@ int nq_pf_post(const float* y, const float* zd, const int32_t* pt, const int32_t
     NQ_REQUIRE(y && zd && pt && pe && prw && table && out, "nq_pf_post: null pointer");
     NQ_SHAPE_OK("nq_pf_post");
     NQ_REQUIRE(nq::aligned16(y) && nq::aligned16(out), "nq_pf_post: y and out must be 16-byte aligned");
-    nq::pf_post_kernel<<<R, 256, 0, (cudaStream_t)stream>>>(y, zd, pt, pe, (const __half*)prw, table, out, H, I);
+    nq::pf_post_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>(y, zd, pt, pe, (const __half*)prw, table, out, H, I);
     return nq::check_launch("nq_pf_post");
 }
 
@@ -291,7 +324,7 @@ int nq_pf_combine(const float* y, const float* zd, const int32_t* pos, const int
     NQ_REQUIRE(y && zd && pos && sel && rw && table && out, "nq_pf_combine: null pointer");
     NQ_SHAPE_OK("nq_pf_combine");
     NQ_REQUIRE(nq::aligned16(y) && nq::aligned16(out), "nq_pf_combine: y and out must be 16-byte aligned");
-    nq::pf_combine_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(y, zd, pos, sel, (const __half*)rw, table, out, topk, E, H, I);
+    nq::pf_combine_kernel<<<T, nq::pf_threads(H), 0, (cudaStream_t)stream>>>(y, zd, pos, sel, (const __half*)rw, table, out, topk, E, H, I);
     return nq::check_launch("nq_pf_combine");
 }
 

@@ -36,6 +36,147 @@ __device__ __forceinline__ void store4h(__half* p, const float (&v)[4])
     *(uint2*)p = u;
 }
 
+// The same transform for eight 128-vectors per warp: lanes 4 v .. 4 v + 3 hold vector v, 32 elements each (lane bits
+// and register bits are index bits of the vector, see the maps below).  Five of the seven butterfly stages stay inside a lane; two cross lanes (8 shuffles per vector
+// instead of 20), which is what the HBM-bound prefill passes need to stay off the shuffle pipe.
+__device__ __forceinline__ void wht128_x8(float (&v)[32], int lane)
+{
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1)
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (!(i & h))
+            {
+                const float a = v[i], b = v[i | h];
+                v[i] = a + b; v[i | h] = a - b;
+            }
+#pragma unroll
+    for (int m = 1; m < 4; m <<= 1)
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+        {
+            const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
+            v[i] = (lane & m) ? o - v[i] : v[i] + o;
+        }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= 0.08838834764831845f;
+}
+// Which 32 elements of its vector a lane holds is free (any assignment of the 7 index bits to 5 register bits and 2
+// lane bits gives the same transform), so it is chosen for coalescing: the 4 lanes of a vector access adjacent pieces.
+//   map H (fp16 arrays, 16-byte accesses): register 8 j + e of lane q = element 32 j + 8 q + e   (j < 4, e < 8)
+//   map F (fp32 arrays, 16-byte accesses; fp16 vectors alongside them by 8-byte accesses):
+//                                          register 4 j + e of lane q = element 16 j + 4 q + e   (j < 8, e < 4)
+// p points at the vector's first element, q = lane & 3.
+__device__ __forceinline__ void load32h_mapH(const __half* p, int q, float (&f)[32])
+{
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        const uint4 u = *(const uint4*)(p + 32 * j + 8 * q);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+        {
+            const __half2 h = *(const __half2*)&w[i];
+            f[8 * j + 2 * i] = __low2float(h); f[8 * j + 2 * i + 1] = __high2float(h);
+        }
+    }
+}
+__device__ __forceinline__ void store32h_mapH(__half* p, int q, const float (&v)[32])
+{
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+        {
+            const __half2 h = __floats2half2_rn(v[8 * j + 2 * i], v[8 * j + 2 * i + 1]);
+            w[i] = *(const uint32_t*)&h;
+        }
+        *(uint4*)(p + 32 * j + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+__device__ __forceinline__ void load32f_mapF(const float* p, int q, float (&f)[32])
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+    {
+        const float4 u = *(const float4*)(p + 16 * j + 4 * q);
+        f[4 * j] = u.x; f[4 * j + 1] = u.y; f[4 * j + 2] = u.z; f[4 * j + 3] = u.w;
+    }
+}
+__device__ __forceinline__ void store32f_mapF(float* p, int q, const float (&v)[32])
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j) *(float4*)(p + 16 * j + 4 * q) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+}
+__device__ __forceinline__ void load32h_mapF(const __half* p, int q, float (&f)[32])
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+    {
+        const uint2 u = *(const uint2*)(p + 16 * j + 4 * q);
+        const __half2 a = *(const __half2*)&u.x, b = *(const __half2*)&u.y;
+        f[4 * j] = __low2float(a); f[4 * j + 1] = __high2float(a); f[4 * j + 2] = __low2float(b); f[4 * j + 3] = __high2float(b);
+    }
+}
+__device__ __forceinline__ void store32h_mapF(__half* p, int q, const float (&v)[32])
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+    {
+        const __half2 a = __floats2half2_rn(v[4 * j], v[4 * j + 1]), b = __floats2half2_rn(v[4 * j + 2], v[4 * j + 3]);
+        uint2 u; u.x = *(const uint32_t*)&a; u.y = *(const uint32_t*)&b;
+        *(uint2*)(p + 16 * j + 4 * q) = u;
+    }
+}
+
+// fused forms (no staging array): v = x * s for packed fp16 x (map H); v *= s, v += z * s, sum v * s for an fp16 vector s (map F)
+__device__ __forceinline__ void load16w_mapH(const __half* p, int q, uint32_t (&w)[16])
+{
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        const uint4 u = *(const uint4*)(p + 32 * j + 8 * q);
+        w[4 * j] = u.x; w[4 * j + 1] = u.y; w[4 * j + 2] = u.z; w[4 * j + 3] = u.w;
+    }
+}
+__device__ __forceinline__ void mul32h_mapH(const uint32_t (&xw)[16], const __half* sp, int q, float (&v)[32])
+{
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        const uint4 u = *(const uint4*)(sp + 32 * j + 8 * q);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+        {
+            const __half2 a = *(const __half2*)&xw[4 * j + i], b = *(const __half2*)&w[i];
+            v[8 * j + 2 * i] = __low2float(a) * __low2float(b); v[8 * j + 2 * i + 1] = __high2float(a) * __high2float(b);
+        }
+    }
+}
+template <class F>
+__device__ __forceinline__ void each32h_mapF(const __half* p, int q, F&& f)
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+    {
+        const uint2 u = *(const uint2*)(p + 16 * j + 4 * q);
+        const __half2 a = *(const __half2*)&u.x, b = *(const __half2*)&u.y;
+        f(4 * j, __low2float(a)); f(4 * j + 1, __high2float(a)); f(4 * j + 2, __low2float(b)); f(4 * j + 3, __high2float(b));
+    }
+}
+__device__ __forceinline__ void scale32h_mapF(const __half* p, int q, float (&v)[32]) { each32h_mapF(p, q, [&](int i, float s) { v[i] *= s; }); }
+__device__ __forceinline__ void axpy32h_mapF(const __half* p, int q, float z, float (&v)[32]) { each32h_mapF(p, q, [&](int i, float s) { v[i] += z * s; }); }
+__device__ __forceinline__ float dot32h_mapF(const __half* p, int q, const float (&v)[32])
+{
+    float d = 0.f;
+    each32h_mapF(p, q, [&](int i, float s) { d += v[i] * s; });
+    return d;
+}
+
 __device__ __forceinline__ float silu(float g) { return g / (1.f + __expf(-g)); }
 
 }  // namespace nq
