@@ -67,6 +67,28 @@ def fit_beta(levels, bias, E, topk, target=0.63):
     return 0.5 * (lo + hi)
 
 
+def fixed_bias(E, n_fixed, seed):
+    """indicator (1 / 0) of n_fixed seeded 'fixed' experts, to be scaled by fit_share"""
+    g = torch.Generator().manual_seed(seed)
+    b = torch.zeros(E)
+    b[torch.randperm(E, generator=g)[:n_fixed]] = 1.0
+    return b
+
+
+def fit_share(bias, E, topk, target=0.5, samples=2048, seed=4321):
+    """bias strength for which the experts with bias > 0 take about `target` of the picks"""
+    lo, hi = 0.0, 8.0
+    hot = bias > 0
+    for _ in range(20):
+        mid = 0.5 * (lo + hi)
+        sel, _ = routing(samples, E, topk, seed, bias, mid)
+        if float(hot[sel].float().mean()) < target:
+            lo = mid
+        else:
+            hi = mid
+    return 0.5 * (lo + hi)
+
+
 def build_layer(cfg, levels, seed=0, dev="cuda", Bmax=4, owned=None, masked=(), nm_frac=0.5):
     """Experts + MoELayer.  owned: expert ids resident on this GPU (others stay at level 0 and get no planes)."""
     E, topk, H, I = cfg["E"], cfg["topk"], cfg["H"], cfg["I"]
