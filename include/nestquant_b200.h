@@ -179,6 +179,49 @@ int nq_moe_forward_static(const void* x, const int64_t* sel, const void* rw, con
                           int B, int topk, int E, int H, int I, int nm_gu, int nm_dn, int ks_gu, int ks_dn,
                           int32_t* hits, void* stream);
 
+/* ---- promotion engine (host side) -------------------------------------------------------------------------------
+ * One engine per GPU process, reading that process's record file (fixed-size records, see nestquant_b200/p4rec.py).
+ * Replaces the torch-extension class Engine of streaming/nqstream.cu:46-283 (upgrade / post / poll / cancel /
+ * tier_load / tier_drop / stats / close, same meaning):
+ *   upgrade  record `rec` -> pinned host entry (drive read, or a hit in the host cache / RAM tier) -> device `slot`
+ *            -> `row` into stage_row -> `seq` into seq_entry, in that order on the engine's own side stream
+ *   post     row and sequence number only (demotion)
+ *   poll     operations whose device writes have completed: hit = the bytes were already in host memory;
+ *            t_read_s / t_done_s = seconds from the call to bytes-in-host-memory / device-writes-done.
+ *            A failed read reports hit 0, t_read_s < 0 (-errno, or -1 for a short read), t_done_s -1 and never posts
+ *            the row; a cancelled operation reports t_read_s = t_done_s = -1e9
+ *   cancel   best effort: drops an operation that has touched neither a drive nor the device yet
+ *   tier_load / tier_drop   pinned RAM copy of chosen records (read once, blocking); upgrades of those skip the drive
+ * Operations start in arrival order; the caller keeps at most one operation per expert outstanding.  Calls return
+ * at once (tier_load and close excepted).  device < 0 runs the engine against host memory (slot, stage_row and
+ * seq_entry are then host pointers): the mode the CPU tests use.  alt_path = an identical copy of the file on a second
+ * drive ("" or NULL for none); each read goes to the drive with fewer reads in flight (caps qd, qd_alt).
+ * Environment (host-side fault injection, as the reference): NQ_FAULT_READ_MS = minimum spacing of drive reads,
+ * NQ_FAULT_FAIL_PPM = share of completed reads reported as failed. */
+typedef struct NqEngine NqEngine;
+typedef struct { int64_t tag; int32_t hit; double t_read_s, t_done_s; } NqEngineDone;
+typedef struct
+{
+    int64_t upgrades, posts, host_hits, bytes_read, fault_injected, cancelled, device_errors;
+    int64_t queued, waiting, reading, copying;                 /* operations not yet seen / waiting / reading / copying */
+    int64_t drive_reads[2], drive_bytes[2], drive_inflight[2], drive_qd[2];
+    double drive_read_s[2];
+    int64_t drives, n_host, tier_state, tier_recs, tier_hits, tier_bytes;   /* tier_state: 0 none, 1 active, 2 dropping, 3 dropped */
+    double now_s;
+} NqEngineStats;
+
+int nq_engine_open(const char* path, const char* alt_path, size_t rec_bytes, int n_host, int qd, int qd_alt, int device,
+                   NqEngine** out);
+int nq_engine_upgrade(NqEngine* e, int64_t tag, int64_t rec, void* slot, void* stage_row, const int64_t* row /* [20] */,
+                      void* seq_entry, int32_t seq);
+int nq_engine_post(NqEngine* e, int64_t tag, void* stage_row, const int64_t* row /* [20] */, void* seq_entry, int32_t seq);
+int nq_engine_cancel(NqEngine* e, int64_t tag);
+int nq_engine_poll(NqEngine* e, NqEngineDone* out, int max);        /* returns the number of entries written */
+int nq_engine_tier_load(NqEngine* e, const int64_t* recs, int n);   /* returns n */
+int nq_engine_tier_drop(NqEngine* e);
+int nq_engine_stats(NqEngine* e, NqEngineStats* out);
+int nq_engine_close(NqEngine* e);
+
 #ifdef __cplusplus
 }
 #endif

@@ -32,6 +32,19 @@ class NqMoeForward(C.Structure):
                                    "which")])
 
 
+class NqEngineDone(C.Structure):
+    _fields_ = [("tag", _i64), ("hit", C.c_int32), ("t_read_s", C.c_double), ("t_done_s", C.c_double)]
+
+
+class NqEngineStats(C.Structure):
+    _fields_ = ([(n, _i64) for n in ("upgrades", "posts", "host_hits", "bytes_read", "fault_injected", "cancelled",
+                                     "device_errors", "queued", "waiting", "reading", "copying")] +
+                [(n, _i64 * 2) for n in ("drive_reads", "drive_bytes", "drive_inflight", "drive_qd")] +
+                [("drive_read_s", C.c_double * 2)] +
+                [(n, _i64) for n in ("drives", "n_host", "tier_state", "tier_recs", "tier_hits", "tier_bytes")] +
+                [("now_s", C.c_double)])
+
+
 # name -> (restype, argtypes); mirrors include/nestquant_b200.h one to one
 SIGNATURES = {
     "nq_last_error": (C.c_char_p, []),
@@ -54,6 +67,15 @@ SIGNATURES = {
     "nq_moe_forward": (_i, [C.POINTER(NqMoeForward), _p]),
     "nq_moe_static_scratch_bytes": (_sz, []),
     "nq_moe_forward_static": (_i, [_p, _p, _p, _p, _p] + [_i] * 9 + [_p, _p]),
+    "nq_engine_open": (_i, [C.c_char_p, C.c_char_p, _sz, _i, _i, _i, _i, C.POINTER(_p)]),
+    "nq_engine_upgrade": (_i, [_p, _i64, _i64, _p, _p, C.POINTER(_i64), _p, C.c_int32]),
+    "nq_engine_post": (_i, [_p, _i64, _p, C.POINTER(_i64), _p, C.c_int32]),
+    "nq_engine_cancel": (_i, [_p, _i64]),
+    "nq_engine_poll": (_i, [_p, C.POINTER(NqEngineDone), _i]),
+    "nq_engine_tier_load": (_i, [_p, C.POINTER(_i64), _i]),
+    "nq_engine_tier_drop": (_i, [_p]),
+    "nq_engine_stats": (_i, [_p, C.POINTER(NqEngineStats)]),
+    "nq_engine_close": (_i, [_p]),
 }
 
 _lib = None

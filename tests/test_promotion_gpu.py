@@ -92,3 +92,70 @@ def test_promotions_race_a_captured_graph():
         assert rl <= 5e-4, (step, level, rl)
     side.synchronize()
     assert lags and max(lags) <= 2 and len(cache) > 3       # switches landed, several distinct level sets were checked
+
+
+def test_engine_promotes_from_a_record_file(tmp_path):
+    """The host engine end to end on the GPU: records in a file -> pinned host cache -> slots -> staged rows -> sequence
+    numbers, applied by the mailbox of a captured layer call; outputs follow the oracle at the levels that are live."""
+    from nestquant_b200 import moe, p4rec
+    from nestquant_b200.engine import Engine, write_records
+    H, I, NE, topk, B = 1024, 512, 6, 3, 2
+    exs = [moe.Expert(H, I, seed=90 + i, rk_gu=0, rk_dn=7, var=True, sv=0.02) for i in range(NE)]
+    exs_o = [expert_to_oracle(e) for e in exs]
+    lay = p4rec.layout(exs[0], H, I)
+    path = str(tmp_path / "rank0.bin")
+    write_records(path, [p4rec.pack(e, lay, pin=False) for e in exs])
+    for e in exs:                                           # resident copy keeps only the base
+        for p in (e.gu, e.dn):
+            p.p4 = torch.zeros(1, dtype=torch.int32, device="cuda"); p.d4 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    L = moe.MoELayer(NE, H, I, Bmax=B, topk=topk)
+    MB = moe.Mailbox(L)
+    for e in range(NE):
+        L.set(e, exs[e], 2)
+    pool = p4rec.SlotPool(4, lay["rec_bytes"])
+    eng = Engine(path, lay["rec_bytes"], 3, 2, torch.cuda.current_device())
+    g = torch.Generator().manual_seed(3)
+    sel = torch.stack([torch.randperm(NE, generator=g)[:topk] for _ in range(B)])
+    rw = torch.softmax(torch.randn(B, topk, generator=g), 1).half()
+    x = torch.randn(B, H, generator=g).bfloat16().half()
+    G = L.capture(B, with_mailbox=MB)
+    G.x.copy_(x); G.sel.copy_(sel); G.rw.copy_(rw)
+
+    def settle(tags):
+        got, t0 = [], __import__("time").time()
+        while len(got) < len(tags) and __import__("time").time() - t0 < 20:
+            got += eng.poll()
+        assert sorted(t for t, *_ in got) == sorted(tags), (got, eng.stats())
+        G.replay(); torch.cuda.synchronize()                # this replay's mailbox applies the rows
+        return got
+
+    def check(levels):
+        ref = O.moe_ref(exs_o, levels, x.numpy(), sel.numpy(), rw.numpy())
+        ma, rl = layer_errors(G.out.cpu().numpy(), ref)
+        assert rl <= 5e-4, (levels, rl)
+
+    G.replay(); torch.cuda.synchronize(); check([2] * NE)
+    ups = [1, 4, 2]
+    for i, e in enumerate(ups):                             # three promotions through two reader threads
+        MB.hseq[e] += 1
+        pool.slot_of[e] = pool.free.pop()
+        eng.upgrade(e, e, pool.slot_ptr(pool.slot_of[e]), MB.stage[e].data_ptr(), p4rec.row(exs[e], lay, pool.slot_ptr(pool.slot_of[e]), moe.entry),
+                    MB.seq[e:e + 1].data_ptr(), MB.hseq[e])
+    res = settle(ups)
+    assert all(tr >= 0 and te >= tr for _, _, tr, te in res) and all(MB.done(e) for e in ups)
+    check([4 if e in ups else 2 for e in range(NE)])
+    MB.hseq[4] += 1                                         # demotion: row only
+    eng.post(104, MB.stage[4].data_ptr(), moe.entry(exs[4], 2), MB.seq[4:5].data_ptr(), MB.hseq[4])
+    settle([104])
+    check([4 if e in (1, 2) else 2 for e in range(NE)])
+    pool.buf[pool.slot_of[4]].fill_(0xAB); pool.release(4)  # the freed slot may be scribbled over
+    MB.hseq[4] += 1                                         # and promoted again: the record is still in the host cache
+    pool.slot_of[4] = pool.free.pop()
+    eng.upgrade(204, 4, pool.slot_ptr(pool.slot_of[4]), MB.stage[4].data_ptr(), p4rec.row(exs[4], lay, pool.slot_ptr(pool.slot_of[4]), moe.entry),
+                MB.seq[4:5].data_ptr(), MB.hseq[4])
+    (_, hit, _, _), = settle([204])
+    assert hit
+    check([4 if e in ups else 2 for e in range(NE)])
+    st = eng.stats()
+    assert st["upgrades"] == 4 and st["host_hits"] == 1 and st["posts"] == 1 and st["device_errors"] == 0
+    eng.close()
