@@ -55,6 +55,8 @@ def row(ex, lay, slot_ptr, entry):
     r[2], r[3], r[6], r[7] = (slot_ptr + s[k][0] for k in ("gu.p4", "gu.d4", "dn.p4", "dn.d4"))
     if getattr(ex, "rg", 0) + getattr(ex, "rd", 0):
         r[15] = slot_ptr + s["lr4"][0]
+    if hasattr(ex, "sc"):
+        r[9] = ex.sc[4].data_ptr()       # level-4 scale vectors of a loaded resident file (nestquant_b200/resident.py)
     return r
 
 
