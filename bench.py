@@ -44,6 +44,9 @@ SEED = 20240
 NCU_TRAFFIC_RATIO = 1.037
 
 
+_JSON_OUT = sys.stdout
+
+
 def measured_peak_gbs():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -164,7 +167,7 @@ def run_reference(args):
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"first {picks} picks of one token per step (decode + fp32 matmuls), {args.steps} steps"},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=_JSON_OUT, flush=True)
 
 
 def moe_bytes(H, I, level):
@@ -289,6 +292,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    # stdout carries the one JSON line and nothing else: libraries that print there (NCCL's version banner) go to stderr
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
         return run_reference(args)
 
@@ -474,7 +482,7 @@ def main():
             ref_us = oracle_step(exs, levels, r1["xs"][i].numpy(), sel_host[i].numpy(), rw_host[i].numpy()) * 1e6
             line["cpu_baseline"] = {"value": r1["nbytes"][i] / ref_us / 1e3, "unit": UNIT, "cores": O.lib().nqo_threads(), "kind": "port",
                                     "sample": "one full 1-token step (8 experts: dense decode + fp32 matmuls)", "layer_us": ref_us}
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=_JSON_OUT, flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
