@@ -125,14 +125,17 @@ def pf_hits(counts, hits_ptr):
     check(lib().nq_pf_hits(ptr(counts), hits_ptr, counts.numel(), current_stream()), "pf_hits")
 
 
-def default_ksplit(B, H, I):
-    """k-slices per strip (gate|up, down) for a B-token call: few tokens need more slices to fill 148 SMs"""
+def default_ksplit(B, H, I, share=1.0):
+    """k-slices per strip (gate|up, down) for a B-token call: few tokens need more slices to fill 148 SMs.
+    share: fraction of the layer's experts resident on this GPU (expert parallelism: 1 / ranks) - a rank that serves only
+    a few of a token's picks cuts finer."""
     def pick(chunks, want):
-        for k in (want, 6, 4, 3, 2, 1):
+        for k in (want, 8, 6, 4, 3, 2, 1):
             if k <= want and chunks % k == 0:
                 return k
         return 1
-    want_gu, want_dn = (4, 2) if B <= 2 else (2, 1) if B <= 8 else (1, 1)
+    load = B * share
+    want_gu, want_dn = (8, 4) if load <= 0.5 else (4, 2) if load <= 2 else (2, 1) if load <= 8 else (1, 1)
     return pick(H // 128, want_gu), pick(I // 128, want_dn)
 
 

@@ -257,9 +257,10 @@ class MoELayer:
 
     Rows are flipped in place (`set`, or a Mailbox), which keeps a captured CUDA graph valid."""
 
-    def __init__(s, E, H, I, nm_gu=0, nm_dn=0, Bmax=4, topk=8, G=4, dev="cuda", mod=None, ksplit=None):
+    def __init__(s, E, H, I, nm_gu=0, nm_dn=0, Bmax=4, topk=8, G=4, dev="cuda", mod=None, ksplit=None, share=1.0):
         """ksplit: optional (gate|up, down) k-slices per strip to size the workspaces for, when calls will override
-        the per-token-count default through cfg_gu / cfg_dn."""
+        the per-token-count default through cfg_gu / cfg_dn.  share: fraction of the experts resident on this GPU (1 / ranks
+        under expert parallelism); it only steers the default k-split."""
         s.M = mod or _ext
         s.E, s.H, s.I, s.nm_gu, s.nm_dn, s.G, s.Bmax, s.topk = E, H, I, nm_gu, nm_dn, G, Bmax, topk
         s.table = torch.zeros(E, TBL_W, dtype=torch.int64, device=dev)
@@ -267,7 +268,8 @@ class MoELayer:
         s.hits_ptr = 0      # set to a (host-mapped) int32 [E] pointer to export routing hits
         s.cfg_gu = s.cfg_dn = None     # [k-slices per strip]; None = chosen from the token count of each call
         # workspaces sized for the deepest k-split any call shape can ask for
-        ws = [s.M.moe_workspace(b, topk, H, I, *s.M.default_ksplit(b, H, I)) for b in range(1, Bmax + 1)]
+        s.share = share
+        ws = [s.M.moe_workspace(b, topk, H, I, *s.M.default_ksplit(b, H, I, share)) for b in range(1, Bmax + 1)]
         if ksplit is not None:
             ws.append(s.M.moe_workspace(Bmax, topk, H, I, *ksplit))
         n = {k: max(w[k] for w in ws) for k in ws[0]}
@@ -303,7 +305,7 @@ class MoELayer:
         B = x.shape[0]
         assert B <= s.Bmax and sel.shape[1] == s.topk, f"layer was built for up to {s.Bmax} tokens, top-{s.topk}"
         out = s.out[:B] if out is None else out
-        ks = s.M.default_ksplit(B, s.H, s.I)
+        ks = s.M.default_ksplit(B, s.H, s.I, s.share)
         s.M.moe_forward(x, sel, rw, s.table if table is None else table, out, s.acc_gu, s.h, s.acc_d, s.cnt_gu, s.cnt_d,
                         s.wq, s.I, s.nm_gu, s.nm_dn, cfg_gu or s.cfg_gu or [ks[0]], cfg_dn or s.cfg_dn or [ks[1]], s.G,
                         force_level, which, s.hits_ptr, s.zd, s.cnt_h)

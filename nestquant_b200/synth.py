@@ -93,7 +93,8 @@ def build_layer(cfg, levels, seed=0, dev="cuda", Bmax=4, owned=None, masked=(), 
     """Experts + MoELayer.  owned: expert ids resident on this GPU (others stay at level 0 and get no planes)."""
     E, topk, H, I = cfg["E"], cfg["topk"], cfg["H"], cfg["I"]
     nm_gu, nm_dn = max(1, int(H // 128 * nm_frac)), max(1, int(I // 128 * nm_frac))
-    L = moe.MoELayer(E, H, I, nm_gu if masked else 0, nm_dn if masked else 0, Bmax=Bmax, topk=topk, dev=dev)
+    L = moe.MoELayer(E, H, I, nm_gu if masked else 0, nm_dn if masked else 0, Bmax=Bmax, topk=topk, dev=dev,
+                     share=1.0 if owned is None else len(owned) / E)
     experts = {}
     for e in (range(E) if owned is None else owned):
         if levels[e] <= 0:
