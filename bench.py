@@ -203,9 +203,9 @@ def prefill_pieces(L, x, sel, rw):
     acc_g, acc_u = torch.empty(P, I, dtype=f32, device=dev), torch.empty(P, I, dtype=f32, device=dev)
     hbuf, y = torch.empty(P, I, dtype=f16, device=dev), torch.empty(P, H, dtype=f32, device=dev)
     out = torch.empty(T, H, dtype=f32, device=dev)
-    steps = [("pf_pre", lambda: M.pf_pre(x, pt, pe, L.table, xg, xu, zg, I)),
+    steps = [("pf_pre", lambda: M.pf_pre(x, pt, pe, L.table, xg, xu, zg, I, kperm=True)),
              ("pf_gemm gate|up", lambda: M.pf_gemm(L.table, plan, xg, xu, acc_g, acc_u, H, I, L.nm_gu, L.nm_dn, False, status)),
-             ("pf_mid", lambda: M.pf_mid(acc_g, acc_u, zg, pe, L.table, hbuf, zd, H, I)),
+             ("pf_mid", lambda: M.pf_mid(acc_g, acc_u, zg, pe, L.table, hbuf, zd, H, I, kperm=True)),
              ("pf_gemm down", lambda: M.pf_gemm(L.table, plan, hbuf, None, y, None, H, I, L.nm_gu, L.nm_dn, True, status)),
              ("pf_combine", lambda: M.pf_combine(y, zd, pos, sel, rw, L.table, out, I))]
     res = {}

@@ -78,15 +78,17 @@ int nq_promote(void* slot, const void* host_record, size_t record_bytes, int64_t
 
 /* xg[p] = fp16(WHT128(x[pt[p]] * su_g)), xu[p] likewise with su_u, both [R][H]; zg[p][r] = x . V_gu[r].
  * Pairs of level-0 experts are skipped (their rows are left untouched).
+ * kperm != 0 writes xg / xu in the k order nq_pf_gemm reads: inside every 16 consecutive k, position 4 i + {0, 1}
+ * holds k = 2 i + {0, 1} and position 4 i + {2, 3} holds k = 8 + 2 i + {0, 1} (i < 4); 0 = plain order (the reference's).
  * Replaces pf_pre() (sm120/nqmoe.cu:1081-1117,1258-1267). */
 int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const int64_t* table, void* xg, void* xu, float* zg,
-              int H, int I, void* stream);
+              int H, int I, int kperm, void* stream);
 
 /* acc_g, acc_u fp32 [R][I] (GEMM outputs) -> h fp16 [R][I] = WHT_w(silu(g) u su_d), g = WHT128(acc_g) sv_g + low rank,
- * w = 128 or the expert's 512-wide rotation; zd[p][r] = (silu(g) u) . V_dn[r].
+ * w = 128 or the expert's 512-wide rotation; zd[p][r] = (silu(g) u) . V_dn[r].  kperm: k order of h as for nq_pf_pre.
  * Replaces pf_mid() (sm120/nqmoe.cu:1118-1203,1268-1277). */
 int nq_pf_mid(const float* acc_g, const float* acc_u, const float* zg, const int32_t* pe, int R, const int64_t* table, void* h,
-              float* zd, int H, int I, void* stream);
+              float* zd, int H, int I, int kperm, void* stream);
 
 /* out[pt[p]] += prw[p] * (WHT128(y[p]) * sv_o + low rank), y fp32 [R][H]; atomic adds into a caller-zeroed out.
  * Replaces pf_post() (sm120/nqmoe.cu:1204-1240,1278-1287). */
@@ -98,14 +100,15 @@ int nq_pf_post(const float* y, const float* zd, const int32_t* pt, const int32_t
 int nq_pf_combine(const float* y, const float* zd, const int32_t* pos, const int64_t* sel, const void* rw, int T, int topk,
                   const int64_t* table, int E, float* out, int H, int I, void* stream);
 
-/* Fused prefill GEMM (decode in shared memory -> tcgen05 / TMEM): the replacement of the reference's
+/* Fused prefill GEMM (decode in registers -> weight tiles in tensor memory -> tcgen05.mma): the replacement of the reference's
  * pf_decode + grouped GEMM pair (sm120/moe.py:303-324, sm120/pf_gemm.py:7-34, sm120/nqmoe.cu:1013-1080); the dense fp16
  * weights are never materialised.
  *   nq_pf_plan   from per-expert pair counts (int32 [E], pairs sorted by expert) build the pass list on the device:
- *                a pass = one resident expert x up to 448 of its pairs.  plan: int32 [nq_pf_plan_ints(E, pairs)].
+ *                a pass = one resident expert x up to 384 of its pairs.  plan: int32 [nq_pf_plan_ints(E, pairs)].
  *   nq_pf_gemm   down = 0: acc_g[p] = xg[p] Wg^T, acc_u[p] = xu[p] Wu^T (act0 = xg, act1 = xu fp16 [pairs][H];
  *                out0 = acc_g, out1 = acc_u fp32 [pairs][I]); down = 1: y[p] = h[p] Wd^T (act0 = h fp16 [pairs][I],
- *                out0 = y fp32 [pairs][H], act1 / out1 unused).  Rows of pairs whose expert is not resident are not
+ *                out0 = y fp32 [pairs][H], act1 / out1 unused).  The activation matrices must be in the k order
+ *                nq_pf_pre / nq_pf_mid write with kperm = 1.  Rows of pairs whose expert is not resident are not
  *                written.  status: int32 [1] on the device, set to 1 if a device-side wait timed out (bounded waits;
  *                the outputs are then invalid) - read it after synchronising. */
 int nq_pf_plan_ints(int E, int pairs);

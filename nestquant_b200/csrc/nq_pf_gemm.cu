@@ -3,18 +3,22 @@
 // Replaces the reference's prefill sequence pf_decode -> dense fp16 weights in VRAM -> cuBLAS / Triton grouped GEMM
 // (sm120/moe.py:303-324, sm120/pf_gemm.py, sm120/nqmoe.cu:1013-1080): the dense weights are never written to HBM.
 //
-// One work item = (pass, 128-row weight group): a pass is one expert and up to 448 of its tokens.  Per item a CTA
+// One work item = (pass, 128-row weight group): a pass is one expert and up to 384 of its tokens.  Per item a CTA
 // walks K in blocks of 64:
 //   warp 0        TMA: the tokens' activation tile [ntok x 64] fp16 (SWIZZLE_128B boxes of 64 rows) -> shared memory
-//   warps 2..17   decode: warp (p, s) streams the chunks of parity p of strip s with cp.async, decodes each unit in
-//                 registers (bit-exact fp16) and stores it as two UMMA A tiles [128 x 64] (K-major, no swizzle):
-//                 k-blocks 2 c and 2 c + 1
-//   warp 1        one thread issues tcgen05.mma (M 128 = weight rows, N = tokens, K 16) into a [128 x 512] fp32
-//                 accumulator in TMEM; tcgen05.commit frees the stages.  Token tiles run 2..4 k-blocks ahead
-//                 (as many stages as fit 120 KB), weight tiles 4 stages (two per decode half)
+//   warps 2..17   decode: a warp streams every other chunk of one strip with cp.async, decodes each unit in registers
+//                 (bit-exact fp16) and stores it with tcgen05.st as two weight tiles [128 x 64] in TENSOR MEMORY
+//                 (k-blocks 2 c and 2 c + 1): the m16n8k16-style fragment a lane holds is exactly what the 16x256b
+//                 store shape takes, so a tile costs 4 stores per warp and no shared memory at all
+//   warp 1        one elected lane issues tcgen05.mma with the A operand in tensor memory (M 128 = weight rows, N =
+//                 tokens, K 16) into a [128 x 384] fp32 accumulator, also in tensor memory; tcgen05.commit frees the
+//                 stages.  Token tiles run 3..8 k-blocks ahead (160 KB), weight tiles 4 stages (32 columns each)
 //   warps 2..17   epilogue: tcgen05.ld the accumulator and store fp32 rows acc[pair][128 columns] (coalesced); it runs
 //                 after the first unit of the CTA's next item has been decoded
-// Each decoded weight is used for every token of the pass, so decode cost is paid once per expert (for up to 448
+// A lane's fragment registers of a k-step hold k = 2 t4 + {0, 1} and 8 + 2 t4 + {0, 1}; stored side by side they make
+// the tile's k order inside every 16: position 4 i + {0, 1} = k 2 i + {0, 1}, position 4 i + {2, 3} = k 8 + 2 i + {0, 1}.
+// The activation matrices must be in the same order (nq_pf_pre / nq_pf_mid with kperm = 1).
+// Each decoded weight is used for every token of the pass, so decode cost is paid once per expert (for up to 384
 // tokens).  Tensor-pipe bound by intent; the decode instruction rate is the practical limit.
 // Every mbarrier wait is bounded: on time-out the CTA raises status[0], drains and returns.
 #include <cuda.h>
@@ -33,17 +37,19 @@ namespace nq {
 #ifndef NQ_PF_SPLIT
 #define NQ_PF_SPLIT 256      // token tiles wider than this are multiplied as two column halves
 #endif
-constexpr int kPfTokens = 448;                       // tokens per pass (7 TMA boxes; the accumulator has 512 TMEM columns)
-constexpr int kPfTmemCols = 512;
+constexpr int kPfTokens = 384;                       // tokens per pass = accumulator columns
+constexpr int kPfTmemCols = 512;                     // [0, 384) accumulator, [384, 512) weight tiles
+constexpr int kPfAccCols = 384;
+constexpr int kPfAStages = 4;                        // weight tiles in tensor memory: each unit fills two consecutive stages
+constexpr int kPfACols = 32;                         // [128 lanes x 64 k] fp16 = 32 columns
 constexpr int kPfBoxRows = 64;                       // token rows per TMA box
 constexpr int kPfBoxBytes = kPfBoxRows * 128;        // [64 rows][64 k] fp16
-constexpr int kPfBBoxes = 15;                        // token-tile region: 4 x 3, 3 x 5 or 2 x 7 boxes per stage
-constexpr int kPfAStages = 4;                        // weight tiles: stages 0, 1 filled by the even-chunk warps, 2, 3 by the odd-chunk warps
-constexpr int kPfABytes = 128 * 64 * 2;              // A tile of one k-block
+constexpr int kPfBBoxes = 20;                        // token-tile region: 8 x 2, 5 x 4, 4 x 5 or 3 x 6 boxes per stage
+constexpr int kPfBStages = 8;                        // most token-tile stages
 constexpr int kPfRingDepth = 2;
 constexpr int kPfDecodeWarps = 16;
 constexpr int kPfThreads = 32 * (2 + kPfDecodeWarps);
-constexpr int kPfSmem = kPfBBoxes * kPfBoxBytes + kPfAStages * kPfABytes + kPfDecodeWarps * kPfRingDepth * kStageBytes + 1024 + 256;
+constexpr int kPfSmem = kPfBBoxes * kPfBoxBytes + kPfDecodeWarps * kPfRingDepth * kStageBytes + 1024 + 256;
 constexpr unsigned long long kPfWaitNs = 2000000000ull;   // a wait that lasts 2 s is treated as a hang
 
 struct PfPass { int expert, row0, ntok, pad; };
@@ -138,56 +144,63 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
-// The four K = 16 steps of one 64-wide k-block, issued by one elected lane of a converged warp: A and B descriptors advance by 256 B and 32 B (16-byte units, low word
-// only: shared-memory addresses fit its 14-bit field).  first == 0: the very first MMA overwrites the accumulator.
-__device__ __forceinline__ void tc_mma_kblock(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
-                                              uint32_t first)
+// The four K = 16 steps of one 64-wide k-block, issued by one elected lane of a converged warp.  The weight operand is
+// in tensor memory (8 columns per step), the token operand in shared memory (descriptor advances by 32 B, in 16-byte
+// units on the low word: shared-memory addresses fit its 14-bit field).  first == 0: the first MMA overwrites the
+// accumulator.
+__device__ __forceinline__ void tc_mma_kblock(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t first)
 {
     asm volatile(
-        "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\t.reg .b32 ta, tb;\n\t"
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 db;\n\t.reg .b32 ta, tb;\n\t"
         "elect.sync _|e, 0xffffffff;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
-        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "setp.eq.b32 p, %5, %5;\n\t"
-        "add.u32 ta, %1, 16;\n\tadd.u32 tb, %3, 2;\n\tmov.b64 da, {ta, %2};\n\tmov.b64 db, {tb, %4};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "add.u32 ta, %1, 32;\n\tadd.u32 tb, %3, 4;\n\tmov.b64 da, {ta, %2};\n\tmov.b64 db, {tb, %4};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "add.u32 ta, %1, 48;\n\tadd.u32 tb, %3, 6;\n\tmov.b64 da, {ta, %2};\n\tmov.b64 db, {tb, %4};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+        "setp.eq.b32 p, %4, %4;\n\t"
+        "add.u32 ta, %1, 8;\n\tadd.u32 tb, %2, 2;\n\tmov.b64 db, {tb, %3};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, p;\n\t"
+        "add.u32 ta, %1, 16;\n\tadd.u32 tb, %2, 4;\n\tmov.b64 db, {tb, %3};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, p;\n\t"
+        "add.u32 ta, %1, 24;\n\tadd.u32 tb, %2, 6;\n\tmov.b64 db, {tb, %3};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, p;\n\t"
         "}"
-        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(first) : "memory");
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(first) : "memory");
 }
-// The same for a token tile cut into two column halves with their own accumulator columns: the two accumulation
-// chains alternate, so that an MMA never follows directly on the one it depends on.
-__device__ __forceinline__ void tc_mma_kblock2(uint32_t tmem_d0, uint32_t tmem_d1, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo0, uint32_t b_lo1,
+// The same for a token tile cut into two column halves with their own accumulator columns (alternating chains).
+__device__ __forceinline__ void tc_mma_kblock2(uint32_t tmem_d0, uint32_t tmem_d1, uint32_t tmem_a, uint32_t b_lo0, uint32_t b_lo1,
                                                uint32_t b_hi, uint32_t idesc0, uint32_t idesc1, uint32_t first)
 {
     asm volatile(
-        "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\t.reg .b32 ta, tb;\n\t"
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 db;\n\t.reg .b32 ta, tb;\n\t"
         "elect.sync _|e, 0xffffffff;\n\t"
-        "setp.ne.b32 p, %9, 0;\n\t"
-        "mov.b64 da, {%2, %3};\n\tmov.b64 db, {%4, %6};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
-        "mov.b64 db, {%5, %6};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %8, p;\n\t"
-        "setp.eq.b32 p, %7, %7;\n\t"
-        "add.u32 ta, %2, 16;\n\tadd.u32 tb, %4, 2;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %6};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
-        "add.u32 tb, %5, 2;\n\tmov.b64 db, {tb, %6};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %8, p;\n\t"
-        "add.u32 ta, %2, 32;\n\tadd.u32 tb, %4, 4;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %6};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
-        "add.u32 tb, %5, 4;\n\tmov.b64 db, {tb, %6};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %8, p;\n\t"
-        "add.u32 ta, %2, 48;\n\tadd.u32 tb, %4, 6;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %6};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %7, p;\n\t"
-        "add.u32 tb, %5, 6;\n\tmov.b64 db, {tb, %6};\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %8, p;\n\t"
+        "setp.ne.b32 p, %8, 0;\n\t"
+        "mov.b64 db, {%3, %5};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], db, %6, p;\n\t"
+        "mov.b64 db, {%4, %5};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], db, %7, p;\n\t"
+        "setp.eq.b32 p, %6, %6;\n\t"
+        "add.u32 ta, %2, 8;\n\tadd.u32 tb, %3, 2;\n\tmov.b64 db, {tb, %5};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %6, p;\n\t"
+        "add.u32 tb, %4, 2;\n\tmov.b64 db, {tb, %5};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], [ta], db, %7, p;\n\t"
+        "add.u32 ta, %2, 16;\n\tadd.u32 tb, %3, 4;\n\tmov.b64 db, {tb, %5};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %6, p;\n\t"
+        "add.u32 tb, %4, 4;\n\tmov.b64 db, {tb, %5};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], [ta], db, %7, p;\n\t"
+        "add.u32 ta, %2, 24;\n\tadd.u32 tb, %3, 6;\n\tmov.b64 db, {tb, %5};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %6, p;\n\t"
+        "add.u32 tb, %4, 6;\n\tmov.b64 db, {tb, %5};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%1], [ta], db, %7, p;\n\t"
         "}"
-        ::"r"(tmem_d0), "r"(tmem_d1), "r"(a_lo), "r"(a_hi), "r"(b_lo0), "r"(b_lo1), "r"(b_hi), "r"(idesc0), "r"(idesc1), "r"(first) : "memory");
+        ::"r"(tmem_d0), "r"(tmem_d1), "r"(tmem_a), "r"(b_lo0), "r"(b_lo1), "r"(b_hi), "r"(idesc0), "r"(idesc1), "r"(first) : "memory");
 }
+// 16 lanes x 256 bits of tensor memory from a warp: lane (g, t4) supplies lane g columns 2 t4, 2 t4 + 1 (r0, r1) and
+// lane g + 8, same columns (r2, r3) - the layout of an m16n8 fragment
+__device__ __forceinline__ void tmem_st_16x256b(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3)
+{
+    asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // shared-memory operand descriptor: start address, leading / stride byte offsets (all >> 4), descriptor version 1,
 // layout 0 = no swizzle, 2 = 128-byte swizzle
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout)
@@ -213,30 +226,26 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
 }
 
 // ---------------------------------------------------------------- decode warps
-// A tile layout (K-major, no swizzle): 8 x 16-byte core matrices, 128 B apart along K, 1024 B apart along rows, i.e.
-// byte (row, k) = (row / 8) * 1024 + (k / 8) * 128 + (row % 8) * 16 + (k % 8) * 2.  A lane's fragment register of
-// k-step t (0..3 inside a 64-wide k-block), rows g + 8 (q & 1), k = 16 t + 2 t4 + 8 (q >> 1) lands at
-// strip * 2048 + lane * 4 + constant: conflict-free stores with no address arithmetic.
-
 struct PfShared
 {
-    uint64_t full_b[4], empty_b[4], full_a[kPfAStages], empty_a[kPfAStages], acc_full, acc_empty;
+    uint64_t full_b[kPfBStages], empty_b[kPfBStages], full_a[kPfAStages], empty_a[kPfAStages], acc_full, acc_empty;
     uint32_t tmem_base;
     volatile int abort_flag;
 };
-// The token-tile region (15 boxes) is cut into stages of 3, 5 or 7 boxes (4, 3 or 2 stages) for a pass of nbox boxes
-// per k-block.  Passes with the same stage size share the stage barriers freely; when the stage size changes between
-// two items of a CTA the new stages overlap old ones at other indices, so the producer first waits until every stage
-// of the old layout has been released.
-__device__ __forceinline__ int b_stage_boxes(int nbox) { return nbox <= 3 ? 3 : nbox <= 5 ? 5 : 7; }
-__device__ __forceinline__ int b_stages(int nbox) { return nbox <= 3 ? 4 : nbox <= 5 ? 3 : 2; }
+// The token-tile region (20 boxes) is cut into stages of 2, 4, 5 or 6 boxes (8, 5, 4 or 3 stages) for a pass of nbox
+// boxes per k-block.  Passes with the same stage size share the stage barriers freely; when the stage size changes
+// between two items of a CTA the new stages overlap old ones at other indices, so the producer first waits until every
+// stage of the old layout has been released.
+__device__ __forceinline__ int b_stage_boxes(int nbox) { return nbox <= 2 ? 2 : nbox <= 4 ? 4 : nbox <= 5 ? 5 : 6; }
+__device__ __forceinline__ int b_stages(int nbox) { return nbox <= 2 ? 8 : nbox <= 4 ? 5 : nbox <= 5 ? 4 : 3; }
 
-// A unit is decoded whole (8 k-steps) by one warp: k-steps 0..3 fill the A tile of k-block 2 c, k-steps 4..7 the
+// A unit is decoded whole (8 k-steps) by one warp: k-steps 0..3 fill the weight tile of k-block 2 c, k-steps 4..7 the
 // tile of k-block 2 c + 1.  The sink does the stage hand-over in between: wait until the MMAs that last read the
-// stage are done, store, make the stores visible to the tensor core, signal "full".
+// stage are done, store the fragments, wait for the stores, signal "full".
 struct UnitSink
 {
-    uint8_t* a_tiles; PfShared* sh; uint32_t it0; int strip_off; int lane; bool* ok;
+    uint32_t tmem_a;      // tensor-memory address of the warp's 16 lanes in weight-tile stage 0
+    PfShared* sh; uint32_t it0; int lane; bool* ok;
     template <int T>
     __device__ __forceinline__ void operator()(std::integral_constant<int, T>, const uint32_t (&a)[4]) const
     {
@@ -245,15 +254,16 @@ struct UnitSink
         {
             if (*ok && !mbar_wait(&sh->empty_a[sa], ((it / kPfAStages) & 1u) ^ 1u, &sh->abort_flag)) *ok = false;
             *ok = __shfl_sync(0xffffffffu, (int)*ok, 0) != 0;
+            tc_fence_after();
         }
-        if (*ok)
+        if (*ok)      // warp-uniform
         {
-            uint8_t* dst = a_tiles + sa * kPfABytes + strip_off + lane * 4;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) *(uint32_t*)(dst + (q & 1) * 1024 + (2 * (T & 3) + (q >> 1)) * 128) = a[q];
+            // a[0], a[2]: row g, k = 2 t4 + {0,1} and 8 + 2 t4 + {0,1}; a[1], a[3]: row g + 8
+            tmem_st_16x256b(tmem_a + sa * kPfACols + (T & 3) * 8, a[0], a[2], a[1], a[3]);
             if constexpr ((T & 3) == 3)
             {
-                fence_async_smem();                  // generic-proxy stores -> visible to the tensor core (async proxy)
+                tmem_wait_st();
+                tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->full_a[sa]);
             }
@@ -265,7 +275,7 @@ struct UnitSink
 // other parity), i.e. k-blocks 4 i + 2 GROUP and + 1.  it_base = k-blocks of earlier items.  false = aborted.
 template <bool REFINED, int RC, class Mid>
 __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int C, int NS, int nm, int lane, int group,
-                                             uint8_t* a_tiles, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
+                                             uint32_t tmem_a, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
 {
     unsigned long long fl = ~0ull;
     if (REFINED && P.flags) fl = __ldg((const unsigned long long*)P.flags + strip);
@@ -316,7 +326,7 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
         const uint32_t sign2 = ((vb >> (lane >> 2)) & 1u) * 0x80008000u;
         const uint4 b = *(const uint4*)(st + lane * 16);
         uint32_t wb[6] = {b.x, b.y, b.z, b.w, 0u, 0u};
-        const UnitSink sink{a_tiles, sh, it_base + 2 * (uint32_t)ch, strip % 8 * 2048, lane, &ok};
+        const UnitSink sink{tmem_a, sh, it_base + 2 * (uint32_t)ch, lane, &ok};
         bool refined = false;
         if constexpr (REFINED) refined = (fl >> ch) & 1ull;
 #if NQ_PF_DEBUG == 1 || NQ_PF_DEBUG == 4
@@ -351,9 +361,9 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
 
 template <class Mid>
 __device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int rc, int strip, int C, int NS, int nm, int lane, int group,
-                                            uint8_t* a_tiles, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
+                                            uint32_t tmem_a, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
 {
-#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV>(P, strip, C, NS, nm, lane, group, a_tiles, ring, sh, it_base, mid)
+#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV>(P, strip, C, NS, nm, lane, group, tmem_a, ring, sh, it_base, mid)
     if (level < 4) NQ_RUN(false, 0);
     switch (rc)
     {
@@ -378,14 +388,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* b_tiles = smem;                                  // token tiles [rows][64 k] fp16, 128-byte swizzle (TMA boxes)
-    uint8_t* a_tiles = smem + kPfBBoxes * kPfBoxBytes;        // kPfAStages x [128 rows][64 k] fp16, core-matrix layout
-    uint8_t* rings = a_tiles + kPfAStages * kPfABytes;        // per decode warp: kPfRingDepth plane stages
+    uint8_t* rings = smem + kPfBBoxes * kPfBoxBytes;          // per decode warp: kPfRingDepth plane stages
     PfShared* sh = (PfShared*)(rings + kPfDecodeWarps * kPfRingDepth * kStageBytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0)
     {
-        for (int s = 0; s < 4; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->empty_b[s], 1); }
+        for (int s = 0; s < kPfBStages; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->empty_b[s], 1); }
         for (int s = 0; s < kPfAStages; ++s) { mbar_init(&sh->full_a[s], kPfDecodeWarps / 2); mbar_init(&sh->empty_a[s], 1); }
         mbar_init(&sh->acc_full, 1); mbar_init(&sh->acc_empty, kPfDecodeWarps);
         sh->abort_flag = 0;
@@ -449,7 +458,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             const CUtensorMap* map = up ? &tmap1 : &tmap0;
             bool ok = true;
             if (sbox != last_sbox)
-                for (int s = 0; ok && s < 4; ++s) ok = mbar_wait_warp(&sh->empty_b[s], ((par_b >> s) & 1u) ^ 1u, &sh->abort_flag);
+                for (int s = 0; ok && s < kPfBStages; ++s) ok = mbar_wait_warp(&sh->empty_b[s], ((par_b >> s) & 1u) ^ 1u, &sh->abort_flag);
             last_sbox = sbox;
             for (int kb = 0, s = 0; ok && kb < nkb; ++kb, s = s + 1 == nb ? 0 : s + 1)
             {
@@ -473,8 +482,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             // N <= 256 per instruction: one MMA per k-step, or two of (nearly) equal width
             const int n0 = ntok16 <= NQ_PF_SPLIT ? ntok16 : ((ntok16 / 2 + 15) & ~15), n1 = ntok16 - n0;
             const uint32_t idesc0 = instr_desc(n0), idesc1 = instr_desc(n1 > 0 ? n1 : 16);
-            const uint64_t adesc0 = smem_desc(saddr(a_tiles), 128, 1024, 0), bdesc0 = smem_desc(saddr(b_tiles), 16, 1024, 2);
-            const uint32_t a_lo0 = (uint32_t)adesc0, a_hi = (uint32_t)(adesc0 >> 32), b_lo0 = (uint32_t)bdesc0, b_hi = (uint32_t)(bdesc0 >> 32);
+            const uint64_t bdesc0 = smem_desc(saddr(b_tiles), 16, 1024, 2);
+            const uint32_t b_lo0 = (uint32_t)bdesc0, b_hi = (uint32_t)(bdesc0 >> 32);
             const uint32_t b_step = (uint32_t)(sbox * (kPfBoxBytes >> 4));
             uint32_t s = 0, b_lo = b_lo0;                 // token-tile stage of this k-block and its descriptor
             for (int kb = 0; ok && kb < nkb; ++kb, ++it)
@@ -485,9 +494,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
                 par_b ^= 1u << s;
                 tc_fence_after();
 #if NQ_PF_DEBUG != 2 && NQ_PF_DEBUG != 3
-                const uint32_t a_lo = a_lo0 + sa * (kPfABytes >> 4);
-                if (n1 > 0) tc_mma_kblock2(tmem, tmem + n0, a_lo, a_hi, b_lo, b_lo + (uint32_t)(n0 * 8), b_hi, idesc0, idesc1, (uint32_t)kb);
-                else tc_mma_kblock(tmem, a_lo, a_hi, b_lo, b_hi, idesc0, (uint32_t)kb);
+                const uint32_t ta = tmem + kPfAccCols + sa * kPfACols;
+                if (n1 > 0) tc_mma_kblock2(tmem, tmem + n0, ta, b_lo, b_lo + (uint32_t)(n0 * 8), b_hi, idesc0, idesc1, (uint32_t)kb);
+                else tc_mma_kblock(tmem, ta, b_lo, b_hi, idesc0, (uint32_t)kb);
 #endif
                 tc_commit_elect(&sh->empty_a[sa]);       // both arrive when the MMAs above have read their operands
                 tc_commit_elect(&sh->empty_b[s]);
@@ -498,7 +507,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
         else
         {
             // ---- decode, then epilogue
-            const int dw = warp - 2, half = dw >> 3, sidx = dw & 7;
+            // A warp may touch only the 32 tensor-memory lanes of its quarter (warp % 4): the four decode warps of a
+            // quarter take its two strips x the two chunk parities.
+            const int dw = warp - 2, qd = warp & 3, sub = (dw >> 2) & 1, half = dw >> 3, sidx = 2 * qd + sub;
+            const uint32_t tmem_a = tmem + ((uint32_t)(32 * qd + 16 * sub) << 16) + kPfAccCols;
             const int64_t* row = a.table + (int64_t)ps.expert * kTableWidth;
             const int level = (int)row[0];
             const ProjPlanes P = planes_from_row(row, a.down);
@@ -508,7 +520,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             // of the previous item runs after this item's first unit is decoded: the MMAs of the previous item's last
             // k-blocks finish meanwhile, and the tensor pipe finds tiles waiting when the accumulator is free again.
             auto mid = [&]() { if (have_prev) { epilogue(prev, prev_wg, prev_up, nitem - 1); have_prev = false; } };
-            const bool ok = decode_item(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, half, a_tiles, ring, sh, it, mid);
+            const bool ok = decode_item(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, half, tmem_a, ring, sh, it, mid);
             it += nkb;
             mid();                                   // (an item of fewer than two chunks: its second warp group decodes nothing)
             if (ok) { prev = ps; prev_wg = wg; prev_up = up; have_prev = true; }
@@ -524,7 +536,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
 }
 
 // ---------------------------------------------------------------- pass plan (device side, no host sync)
-// counts[e] = routed pairs of expert e (pairs are sorted by expert).  A pass = one expert x up to 448 of its pairs;
+// counts[e] = routed pairs of expert e (pairs are sorted by expert).  A pass = one expert x up to 384 of its pairs;
 // experts at level 0 get none.  plan: [0] passes, [1] pairs covered, then PfPass records from int 4 on.
 __global__ void pf_plan_kernel(const int* __restrict__ counts, const int64_t* __restrict__ table, int E, int* plan, int max_passes)
 {

@@ -47,7 +47,7 @@ __device__ __forceinline__ float quad_sum(float d)
 }
 // one CTA per pair, one warp per 1024 columns
 __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(const __half* __restrict__ x, const int* __restrict__ pt, const int* __restrict__ pe,
-                                                     const int64_t* __restrict__ table, __half* xg, __half* xu, float* zg, int H, int I)
+                                                     const int64_t* __restrict__ table, __half* xg, __half* xu, float* zg, int H, int I, int kperm)
 {
     const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int64_t* row = table + (int64_t)pe[p] * kTableWidth;
@@ -72,7 +72,8 @@ __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(const __ha
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = 0.f;
             wht128_x8(v, lane);
-            if (live) store32h_mapH((up ? xu : xg) + (size_t)p * H + k, q, v);
+            if (kperm) store32h_mapH_kperm((up ? xu : xg) + (size_t)p * H + k, q, v, live);
+            else if (live) store32h_mapH((up ? xu : xg) + (size_t)p * H + k, q, v);
         }
     }
     const LowRank L = low_rank_of(row, level);
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(const __ha
 
 // one CTA per pair, one warp per 1024 columns; dynamic shared memory: I floats (staging for the 512-wide rotation)
 __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_mid_kernel(const float* __restrict__ acc_g, const float* __restrict__ acc_u, const float* __restrict__ zg,
-                                                     const int* __restrict__ pe, const int64_t* __restrict__ table, __half* h, float* zd, int H, int I)
+                                                     const int* __restrict__ pe, const int64_t* __restrict__ table, __half* h, float* zd, int H, int I, int kperm)
 {
     extern __shared__ float stage[];
     __shared__ float zpart[64][4];
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_mid_kernel(const floa
         wht128_x8(v, lane);
         if (live)
         {
-            if (hw <= 128) store32h_mapF(h + (size_t)p * I + col, q, v);
+            if (hw <= 128) { if (kperm) store32h_mapF_kperm(h + (size_t)p * I + col, q, v); else store32h_mapF(h + (size_t)p * I + col, q, v); }
             else store32f_mapF(stage + col, q, v);
         }
     }
@@ -178,7 +179,8 @@ __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_mid_kernel(const floa
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) o[i] *= rs;
-            store4h(h + (size_t)p * I + blk * 128 + lane * 4, o);
+            if (kperm) store4h_kperm(h + (size_t)p * I + blk * 128, lane, o);
+            else store4h(h + (size_t)p * I + blk * 128 + lane * 4, o);
         }
     }
 }
@@ -281,26 +283,26 @@ extern "C" {
 #define NQ_SHAPE_OK(fn) NQ_REQUIRE(H > 0 && I > 0 && H % 128 == 0 && I % 128 == 0 && H / 128 <= 64 && I / 128 <= 64, fn ": H = %d, I = %d must be multiples of 128, at most 64 * 128", H, I)
 
 int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const int64_t* table, void* xg, void* xu, float* zg,
-              int H, int I, void* stream)
+              int H, int I, int kperm, void* stream)
 {
     NQ_REQUIRE(R >= 0, "nq_pf_pre: R = %d", R);
     if (R == 0) return NQ_OK;
     NQ_REQUIRE(x && pt && pe && table && xg && xu && zg, "nq_pf_pre: null pointer");
     NQ_SHAPE_OK("nq_pf_pre");
     NQ_REQUIRE(nq::aligned16(x) && nq::aligned16(xg) && nq::aligned16(xu), "nq_pf_pre: x, xg, xu must be 16-byte aligned");
-    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>((const __half*)x, pt, pe, table, (__half*)xg, (__half*)xu, zg, H, I);
+    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>((const __half*)x, pt, pe, table, (__half*)xg, (__half*)xu, zg, H, I, kperm);
     return nq::check_launch("nq_pf_pre");
 }
 
 int nq_pf_mid(const float* acc_g, const float* acc_u, const float* zg, const int32_t* pe, int R, const int64_t* table, void* h,
-              float* zd, int H, int I, void* stream)
+              float* zd, int H, int I, int kperm, void* stream)
 {
     NQ_REQUIRE(R >= 0, "nq_pf_mid: R = %d", R);
     if (R == 0) return NQ_OK;
     NQ_REQUIRE(acc_g && acc_u && zg && pe && table && h && zd, "nq_pf_mid: null pointer");
     NQ_SHAPE_OK("nq_pf_mid");
     NQ_REQUIRE(nq::aligned16(acc_g) && nq::aligned16(acc_u) && nq::aligned16(h), "nq_pf_mid: acc_g, acc_u, h must be 16-byte aligned");
-    nq::pf_mid_kernel<<<R, nq::pf_threads(I), (size_t)I * 4, (cudaStream_t)stream>>>(acc_g, acc_u, zg, pe, table, (__half*)h, zd, H, I);
+    nq::pf_mid_kernel<<<R, nq::pf_threads(I), (size_t)I * 4, (cudaStream_t)stream>>>(acc_g, acc_u, zg, pe, table, (__half*)h, zd, H, I, kperm);
     return nq::check_launch("nq_pf_mid");
 }
 

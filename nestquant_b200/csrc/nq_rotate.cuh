@@ -132,6 +132,56 @@ __device__ __forceinline__ void store32h_mapF(__half* p, int q, const float (&v)
     }
 }
 
+// k-permuted fp16 stores for the fused prefill GEMM, whose decode warps write weight fragments to tensor memory in
+// their register order: inside every group of 16 consecutive k, position 4 i + {0, 1} holds k = 2 i + {0, 1} and
+// position 4 i + {2, 3} holds k = 8 + 2 i + {0, 1} (i = 0 .. 3).
+// map H: lane q holds 8 consecutive k of a 16-group (first half for even q, second for odd q); the two lanes of a pair
+// swap two packed words so that each still writes 16 contiguous bytes.
+__device__ __forceinline__ void store32h_mapH_kperm(__half* p, int q, const float (&v)[32], bool live)
+{
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+        {
+            const __half2 h = __floats2half2_rn(v[8 * j + 2 * i], v[8 * j + 2 * i + 1]);
+            w[i] = *(const uint32_t*)&h;
+        }
+        const bool odd = q & 1;
+        // even lane (k 0..7 of the group) keeps words 0, 1 and needs the partner's words 0, 1 (k 8..11);
+        // odd lane (k 8..15) keeps words 2, 3 and needs the partner's words 2, 3 (k 4..7)
+        const uint32_t s0 = __shfl_xor_sync(0xffffffffu, odd ? w[0] : w[2], 1), s1 = __shfl_xor_sync(0xffffffffu, odd ? w[1] : w[3], 1);
+        const uint4 o = odd ? make_uint4(s0, w[2], s1, w[3]) : make_uint4(w[0], s0, w[1], s1);
+        // group base = 32 j + 16 (q >> 1); even lane writes positions 0..7, odd lane positions 8..15
+        if (live) *(uint4*)(p + 32 * j + 16 * (q >> 1) + 8 * (q & 1)) = o;      // every lane takes part in the exchange above
+    }
+}
+// map F: lane q holds k = 4 q .. 4 q + 3 of the 16-group j: two packed words that land at two places
+__device__ __forceinline__ void store32h_mapF_kperm(__half* p, int q, const float (&v)[32])
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+    {
+        const __half2 a = __floats2half2_rn(v[4 * j], v[4 * j + 1]), b = __floats2half2_rn(v[4 * j + 2], v[4 * j + 3]);
+        // k = 4 q + {0,1} -> pair index i = 2 q (mod 4) in half (q >> 1); k = 4 q + {2,3} -> i = 2 q + 1
+        const int half = q >> 1, i0 = (2 * q) & 3;
+        uint32_t* g = (uint32_t*)(p + 16 * j);
+        g[2 * i0 + half] = *(const uint32_t*)&a;
+        g[2 * (i0 + 1) + half] = *(const uint32_t*)&b;
+    }
+}
+// the same permutation for a lane holding 4 consecutive k (element 4 * lane + i of a 128-vector)
+__device__ __forceinline__ void store4h_kperm(__half* vec, int lane, const float (&v)[4])
+{
+    const __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
+    const int q = lane & 3, half = q >> 1, i0 = (2 * q) & 3;
+    uint32_t* g = (uint32_t*)(vec + 16 * (lane >> 2));
+    g[2 * i0 + half] = *(const uint32_t*)&a;
+    g[2 * (i0 + 1) + half] = *(const uint32_t*)&b;
+}
+
 // fused forms (no staging array): v = x * s for packed fp16 x (map H); v *= s, v += z * s, sum v * s for an fp16 vector s (map F)
 __device__ __forceinline__ void load16w_mapH(const __half* p, int q, uint32_t (&w)[16])
 {

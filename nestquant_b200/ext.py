@@ -50,24 +50,25 @@ def pf_decode(table, experts, Wgu, Wdn, H, I, nm_gu, nm_dn, force_level=0):
                              current_stream()), "pf_decode")
 
 
-def pf_pre(x, pt, pe, table, xg, xu, zg, I):
-    """per pair (sorted by expert): xg / xu = fp16(WHT128(x * su_g / su_u)) [R,H], zg = x V_gu^T [R,4]"""
+def pf_pre(x, pt, pe, table, xg, xu, zg, I, kperm=False):
+    """per pair (sorted by expert): xg / xu = fp16(WHT128(x * su_g / su_u)) [R,H], zg = x V_gu^T [R,4].
+    kperm: write the k order the fused pf_gemm reads (see the header); False = the reference's plain order"""
     _need(x, torch.float16, "x"); _need(pt, torch.int32, "pt"); _need(pe, torch.int32, "pe"); _need(table, torch.int64, "table")
     _need(xg, torch.float16, "xg"); _need(xu, torch.float16, "xu"); _need(zg, torch.float32, "zg")
     R, H = pt.numel(), x.shape[1]
     if pe.numel() < R or xg.numel() < R * H or xu.numel() < R * H or zg.numel() < R * 4:
         raise NestQuantError("pf_pre sizes")
-    check(lib().nq_pf_pre(ptr(x), ptr(pt), ptr(pe), R, ptr(table), ptr(xg), ptr(xu), ptr(zg), H, I, current_stream()), "pf_pre")
+    check(lib().nq_pf_pre(ptr(x), ptr(pt), ptr(pe), R, ptr(table), ptr(xg), ptr(xu), ptr(zg), H, I, int(bool(kperm)), current_stream()), "pf_pre")
 
 
-def pf_mid(acc_g, acc_u, zg, pe, table, h, zd, H, I):
+def pf_mid(acc_g, acc_u, zg, pe, table, h, zd, H, I, kperm=False):
     """acc_g / acc_u fp32 [R,I] -> h fp16 [R,I] (rotations, scales, SwiGLU), zd [R,4]"""
     _need(acc_g, torch.float32, "acc_g"); _need(acc_u, torch.float32, "acc_u"); _need(zg, torch.float32, "zg")
     _need(pe, torch.int32, "pe"); _need(table, torch.int64, "table"); _need(h, torch.float16, "h"); _need(zd, torch.float32, "zd")
     R = pe.numel()
     if acc_g.numel() < R * I or acc_u.numel() < R * I or h.numel() < R * I or zd.numel() < R * 4 or zg.numel() < R * 4:
         raise NestQuantError("pf_mid sizes")
-    check(lib().nq_pf_mid(ptr(acc_g), ptr(acc_u), ptr(zg), ptr(pe), R, ptr(table), ptr(h), ptr(zd), H, I, current_stream()), "pf_mid")
+    check(lib().nq_pf_mid(ptr(acc_g), ptr(acc_u), ptr(zg), ptr(pe), R, ptr(table), ptr(h), ptr(zd), H, I, int(bool(kperm)), current_stream()), "pf_mid")
 
 
 def pf_post(y, zd, pt, pe, prw, table, out, I):

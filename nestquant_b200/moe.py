@@ -381,12 +381,12 @@ class MoELayer:
             status = torch.zeros(1, dtype=i32, device=dev)
             xg, xu = torch.empty(P, H, dtype=f16, device=dev), torch.empty(P, H, dtype=f16, device=dev)
             zg, zd = torch.zeros(P, 4, dtype=f32, device=dev), torch.zeros(P, 4, dtype=f32, device=dev)
-            M.pf_pre(x, pt, pe, tb, xg, xu, zg, I)
+            M.pf_pre(x, pt, pe, tb, xg, xu, zg, I, kperm=True)
             acc_g, acc_u = torch.empty(P, I, dtype=f32, device=dev), torch.empty(P, I, dtype=f32, device=dev)
             M.pf_gemm(tb, plan, xg, xu, acc_g, acc_u, H, I, s.nm_gu, s.nm_dn, False, status)
             del xg, xu
             hbuf = torch.empty(P, I, dtype=f16, device=dev)
-            M.pf_mid(acc_g, acc_u, zg, pe, tb, hbuf, zd, H, I)
+            M.pf_mid(acc_g, acc_u, zg, pe, tb, hbuf, zd, H, I, kperm=True)
             del acc_g, acc_u
             y = torch.empty(P, H, dtype=f32, device=dev)
             M.pf_gemm(tb, plan, hbuf, None, y, None, H, I, s.nm_gu, s.nm_dn, True, status)
