@@ -116,6 +116,33 @@ def test_prefill_glm_shape_fused_matches_library_gemm():
     assert layer_errors((2 * yh).cpu().numpy(), y.cpu().numpy())[1] <= 1e-3      # halving fp16 weights is exact up to subnormals
 
 
+def test_prefill_many_tokens_per_expert():
+    """Experts with more tokens than one pass holds (384) and than one MMA is wide (256): several passes per expert,
+    token tiles cut in two column halves; against the library-GEMM path and the oracle."""
+    from nestquant_b200 import moe
+    H, I, NE, topk, T = 256, 384, 3, 2, 900
+    exs = [moe.Expert(H, I, seed=820 + i, rk_gu=(0, 6, 0)[i], rk_dn=7, var=True, sv=0.02) for i in range(NE)]
+    L = moe.MoELayer(NE, H, I, Bmax=1, topk=topk)
+    levels = [4, 2, 4]
+    for e in range(NE):
+        L.set(e, exs[e], levels[e])
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(T, H, generator=g).bfloat16().half()
+    logits = torch.randn(T, NE, generator=g) + torch.tensor([1.5, 0.0, -0.5])
+    tv, sel = logits.topk(topk, dim=1)
+    rw = torch.softmax(tv, 1).half()
+    counts = torch.bincount(sel.reshape(-1), minlength=NE).tolist()
+    assert max(counts) > 768 and any(256 < c <= 384 for c in counts), counts      # 3 passes for one expert, a split tile for another
+    xd, seld, rwd = x.cuda(), sel.cuda(), rw.cuda()
+    y_lib = L.prefill(xd, seld, rwd, fused=False)
+    y = L.prefill(xd, seld, rwd)
+    torch.cuda.synchronize()
+    assert layer_errors(y.cpu().numpy(), y_lib.cpu().numpy())[1] <= 1e-4
+    ref = O.moe_ref([expert_to_oracle(e) for e in exs], levels, x.numpy(), sel.numpy(), rw.numpy())
+    ma, rl = layer_errors(y.cpu().numpy(), ref)
+    assert ma <= MAX_ABS_TOL and rl <= 5e-4, (ma, rl)
+
+
 def test_pf_helpers_reject_bad_sizes():
     from nestquant_b200 import ext
     from nestquant_b200.capi import NestQuantError
