@@ -73,8 +73,15 @@ __device__ __forceinline__ bool pick_valid(const MoeArgs& a, int s, int* expert,
 
 // ---------------------------------------------------------------- routing + input rotation
 // grid = B * topk CTAs of 256 threads
+// Programmatic dependent launch: a kernel lets its successor in the stream start launching early (launch_dependents)
+// and the successor blocks (grid_dependency_wait) until the whole predecessor grid has completed and its writes are
+// visible, before it touches anything.  This hides the launch latency between the three kernels of a layer call.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __global__ void __launch_bounds__(256) route_kernel(MoeArgs a)
 {
+    launch_dependents();
     const int S = a.B * a.topk, s = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int e = 0, lv = 0;
     const bool ok = pick_valid(a, s, &e, &lv);
@@ -314,6 +321,8 @@ __global__ void __launch_bounds__(256, NQ_GEMV_MINBLOCKS) gemv_kernel(MoeArgs a)
     extern __shared__ __align__(16) uint8_t smem_ring[];   // [8 warps][kDepth][kStageBytes]
     __shared__ Run run;
     __shared__ int s_item, s_last;
+    launch_dependents();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int S = a.B * a.topk;
     const int N = DOWN ? a.H : 2 * a.I, K = DOWN ? a.I : a.H, C = K / 128, NS = N / 16;
@@ -537,6 +546,21 @@ static int resident_ctas(const void* fn, int threads)
     return sms * (per > 0 ? per : 1);
 }
 
+// launch gemv_kernel<DOWN> as a programmatic dependent of the kernel before it in the stream
+template <int DOWN>
+static int launch_after(int ctas, cudaStream_t st, const MoeArgs& a)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = kGemvSmem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_kernel<DOWN>, a);
+    if (e != cudaSuccess) return fail(NQ_ERR_CUDA, "nq_moe_forward(%s): %s", DOWN ? "down" : "gate|up", cudaGetErrorString(e));
+    return check_launch(DOWN ? "nq_moe_forward(down)" : "nq_moe_forward(gate|up)");
+}
+
 }  // namespace nq
 
 extern "C" {
@@ -591,15 +615,13 @@ int nq_moe_forward(const NqMoeForward* p, void* stream)
     {
         static int ctas = nq::resident_ctas((const void*)nq::gemv_kernel<0>, 256);
         if (ctas <= 0) return nq::fail(NQ_ERR_CUDA, "nq_moe_forward: cannot reserve %d bytes of shared memory", nq::kGemvSmem);
-        nq::gemv_kernel<0><<<ctas, 256, nq::kGemvSmem, st>>>(a);
-        if (int e = nq::check_launch("nq_moe_forward(gate|up)")) return e;
+        if (int e = nq::launch_after<0>(ctas, st, a)) return e;
     }
     if (p->which & 2)
     {
         static int ctas = nq::resident_ctas((const void*)nq::gemv_kernel<1>, 256);
         if (ctas <= 0) return nq::fail(NQ_ERR_CUDA, "nq_moe_forward: cannot reserve %d bytes of shared memory", nq::kGemvSmem);
-        nq::gemv_kernel<1><<<ctas, 256, nq::kGemvSmem, st>>>(a);
-        if (int e = nq::check_launch("nq_moe_forward(down)")) return e;
+        if (int e = nq::launch_after<1>(ctas, st, a)) return e;
     }
     return NQ_OK;
 }
