@@ -2,7 +2,7 @@
 //
 // Replaces moe_forward() of the reference (sm120/nqmoe.cu:858-907 and the kernels it launches, :375-824) with three
 // launches on one stream, all reading routing, levels and plane pointers on the device (graph-capturable):
-//   route_kernel   one CTA per pick: x * su -> WHT128 -> fp16 for the gate and the up half; CTA 0 also groups the picks
+//   route_kernel   one CTA per pick: x * su -> WHT128 -> fp16 for the gate and the up half; one more CTA groups the picks
 //                  into runs (one expert + the tokens that picked it), heaviest level first.
 //   gemv_kernel<0> gate|up: persistent CTAs pull (run, 128-column group, gate/up, k-slice) items; each warp streams one
 //                  16-row strip of packed planes from HBM, decodes it in registers and feeds mma.m16n8k16 with the
@@ -84,8 +84,8 @@ __global__ void __launch_bounds__(256) route_kernel(MoeArgs a)
     launch_dependents();
     const int S = a.B * a.topk, s = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int e = 0, lv = 0;
-    const bool ok = pick_valid(a, s, &e, &lv);
-    if (a.hits && threadIdx.x == 0)
+    const bool ok = s < S && pick_valid(a, s, &e, &lv);
+    if (a.hits && threadIdx.x == 0 && s < S)
     {
         const int64_t es = a.sel[s];
         if (es >= 0 && es < a.E && __half2float(a.rw[s]) != 0.f) atomicAdd(a.hits + es, 1);   // every pick with a weight, any level
@@ -106,9 +106,9 @@ __global__ void __launch_bounds__(256) route_kernel(MoeArgs a)
             store4h(a.xrot + ((size_t)s * 2 + up) * a.H + k, v);
         }
     }
-    if (blockIdx.x != 0) return;
+    if (s != S) return;
 
-    // CTA 0: group the picks into runs.  A run = one expert and up to 8 of its picks in pick order; runs are numbered
+    // The extra CTA (it rotates nothing, so it runs beside the others): group the picks into runs.  A run = one expert and up to 8 of its picks in pick order; runs are numbered
     // by first pick, then ordered level 4 before level 2 (heavier items are handed out first).
     __shared__ int s_exp[NQ_MAX_PICKS], s_lvl[NQ_MAX_PICKS], s_pos[NQ_MAX_PICKS], s_cnt[NQ_MAX_PICKS], s_lead[NQ_MAX_PICKS];
     __shared__ int s_ord[NQ_MAX_PICKS], s_rank[NQ_MAX_PICKS], s_warp[8], s_nruns;
@@ -609,7 +609,7 @@ int nq_moe_forward(const NqMoeForward* p, void* stream)
     a.part_gu = p->acc_gu; a.part_d = p->acc_d; a.zd = p->zd; a.cnt_gu = p->cnt_gu; a.cnt_d = p->cnt_d; a.wq = p->wq; a.out = p->out; a.hits = p->hits;
     cudaStream_t st = (cudaStream_t)stream;
     const int S = p->B * p->topk;
-    nq::route_kernel<<<S, 256, 0, st>>>(a);
+    nq::route_kernel<<<S + 1, 256, 0, st>>>(a);
     if (int e = nq::check_launch("nq_moe_forward(route)")) return e;
     if (p->which & 1)
     {
