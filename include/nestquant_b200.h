@@ -43,8 +43,11 @@ int nq_build_arch(void);
 /* Residual window codes compiled in, bit c = code c: out[0] gate|up, out[1] down.
  * Replaces rk_codes() (sm120/nqmoe.cu:938-940). */
 int nq_rk_codes(int64_t out[2]);
-/* Base window codes compiled in (bit 0 only: the 128-bit ring base).  Replaces the optional bk_codes()
- * that sm120/moe.py:247-249 probes for. */
+/* Base window codes compiled in, bit c = code c: 0 = the 128-bit ring base (2 bits per weight), 1 = the pattern-rate base
+ * of sm120/NQ_RES_V2.md:36-50 (1.75 bits per weight, 112-bit records in the sub-array layout; table field [19] =
+ * bk_gu | bk_dn << 8).  Code 1 is built at level 2 and, at level 4, with the residual codes that build ships with (3 and
+ * 9); the reference kernel has no base code other than 0.  Replaces the optional bk_codes() that sm120/moe.py:247-249
+ * probes for. */
 int nq_bk_codes(int64_t out[2]);
 
 /* Bytes of a residual plane of `nrec` lane records of window code `code` (sm120/moe.py:27-30), or 0 for a bad code. */

@@ -52,7 +52,7 @@ int nq_rk_codes(int64_t out[2])
 int nq_bk_codes(int64_t out[2])
 {
     if (!out) return nq::fail(NQ_ERR_ARG, "nq_bk_codes: null output");
-    out[0] = out[1] = 1;
+    out[0] = out[1] = 3;      // base codes 0 and 1 (code 1 with residual codes 3 and 9 at level 4)
     return NQ_OK;
 }
 size_t nq_plane_bytes(size_t nrec, int code)

@@ -142,11 +142,14 @@ __device__ __forceinline__ UnitConsts consts_level4(uint32_t block_word, uint32_
     return k;
 }
 
-// fp16x2 of lane weights 2 PP and 2 PP + 1.  RES: refined (level 4) unit, RC its residual window code.
-template <bool RES, int RC, int PP>
+// fp16x2 of lane weights 2 PP and 2 PP + 1.  RES: refined (level 4) unit, RC its residual window code, BK the window
+// code of the base stream (0 = 2 bits per weight in 128-bit records; 1 = 1.75 bits per weight in 112-bit records,
+// sm120/NQ_RES_V2.md:36-50: only the base state walk changes).
+template <bool RES, int RC, int PP, int BK = 0>
 __device__ __forceinline__ uint32_t decode_pair(const uint32_t* wb, const uint32_t* wr, const UnitConsts& k)
 {
-    const uint32_t x0 = window16<4 * PP>(wb) * kHashMul, x1 = window16<4 * PP + 2>(wb) * kHashMul;
+    constexpr int b0 = step_offset(2 * PP, BK), b1 = step_offset(2 * PP + 1, BK);
+    const uint32_t x0 = window16<b0>(wb) * kHashMul, x1 = window16<b1>(wb) * kHashMul;
     if constexpr (!RES)
     {
         // 0x6400 + S is the fp16 bit pattern of 1024 + S (S <= 1020)

@@ -209,10 +209,11 @@ struct TokenSink
 
 // One warp, one strip, chunks [c0, c1) (at most 64): stream, decode, multiply.  REFINED: the expert is at level 4.
 // ring: this warp's kDepth stages.
-template <bool REFINED, int RC, int NT>
+template <bool REFINED, int RC, int NT, int BK = 0>
 __device__ __forceinline__ void strip_gemv(const ProjPlanes& P, int strip, int C, int NS, int nm, int c0, int c1, int lane,
                                            float (&acc)[NT][4], const __half* xbase, const int (&xoff)[NT], uint8_t* ring)
 {
+    const size_t base_nrec = (size_t)NS * C * 32;
     unsigned long long fl = ~0ull;
     if (REFINED && P.flags) fl = __ldg((const unsigned long long*)P.flags + strip);
     const size_t res_nrec = (size_t)NS * (P.flags ? nm : C) * 32;
@@ -233,7 +234,7 @@ __device__ __forceinline__ void strip_gemv(const ProjPlanes& P, int strip, int C
         }
     }
     auto issue = [&](int ch, uint8_t* st) {
-        cp_async16(st + lane * 16, (const uint8_t*)(P.base + (unit0 + ch) * 32 + lane));
+        copy_base<BK>(st, P.base, (unit0 + ch) * 32 + lane, base_nrec, lane);
         if constexpr (REFINED)
             if ((fl >> ch) & 1ull) copy_record<RC>(st + 512, P.p4, res_unit(ch) * 32 + lane, res_nrec, lane);
     };
@@ -255,8 +256,8 @@ __device__ __forceinline__ void strip_gemv(const ProjPlanes& P, int strip, int C
         const int rel = ch - c0;
         const uint32_t vb = __shfl_sync(0xffffffffu, rel < 32 ? var_lo : var_hi, rel & 31);
         const uint32_t sign2 = ((vb >> (lane >> 2)) & 1u) * 0x80008000u;
-        const uint4 b = *(const uint4*)(st + lane * 16);
-        uint32_t wb[6] = {b.x, b.y, b.z, b.w, 0u, 0u};
+        uint32_t wb[Pattern<BK>::kWords + 2];
+        read_base<BK>(wb, st, (unit0 + ch) * 32 + lane, lane);
         const TokenSink<NT> sink{acc, xbase, xoff, ch * 128 + (lane & 3) * 2};
         bool refined = false;
         if constexpr (REFINED) refined = (fl >> ch) & 1ull;
@@ -265,10 +266,10 @@ __device__ __forceinline__ void strip_gemv(const ProjPlanes& P, int strip, int C
             const uint32_t dl = __shfl_sync(0xffffffffu, rel < 32 ? dl_lo : dl_hi, rel & 31);
             uint32_t wr[Pattern<RC>::kWords + 2];
             read_record<RC>(wr, st + 512, res_unit(ch) * 32 + lane, lane);
-            decode_words<true, RC>(wb, wr, consts_level4(dl, sign2), lane, sink);
+            decode_words<true, RC, BK>(wb, wr, consts_level4(dl, sign2), lane, sink);
         }
         else
-            decode_words<false, 0>(wb, nullptr, consts_level2(sign2), lane, sink);
+            decode_words<false, 0, BK>(wb, nullptr, consts_level2(sign2), lane, sink);
     }
     cp_async_wait<0>();
 }
@@ -276,7 +277,7 @@ __device__ __forceinline__ void strip_gemv(const ProjPlanes& P, int strip, int C
 // one warp's share of an item: its strip over chunks [c0, c1) for the run's tokens, then the partial sums
 // part[ks][slot][row] of this k-slice
 template <int DOWN, int NT>
-__device__ __forceinline__ void item_gemv(const MoeArgs& a, const Run& run, const ProjPlanes& P, int level, int rc, int nm,
+__device__ __forceinline__ void item_gemv(const MoeArgs& a, const Run& run, const ProjPlanes& P, int level, int rc, int bk, int nm,
                                           int strip, int C, int NS, int c0, int c1, int up, int ks, float* part, int N, int S,
                                           uint8_t* ring)
 {
@@ -295,7 +296,14 @@ __device__ __forceinline__ void item_gemv(const MoeArgs& a, const Run& run, cons
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
 #define NQ_LOOP(REF, RCV) strip_gemv<REF, RCV, NT>(P, strip, C, NS, nm, c0, c1, lane, acc, xbase, xoff, ring)
-    if (level < 4) NQ_LOOP(false, 0);
+#define NQ_LOOP1(REF, RCV) strip_gemv<REF, RCV, NT, 1>(P, strip, C, NS, nm, c0, c1, lane, acc, xbase, xoff, ring)
+    if (bk == 1)        // 112-bit base records, with the residual codes they ship with
+    {
+        if (level < 4) NQ_LOOP1(false, 0);
+        else if (rc == 9) NQ_LOOP1(true, 9);
+        else NQ_LOOP1(true, 3);
+    }
+    else if (level < 4) NQ_LOOP(false, 0);
     else switch (rc)
     {
 #define NQ_CASE(c) case c: if constexpr ((NQ_GEMV_CODES >> c) & 1) { NQ_LOOP(true, c); } break;
@@ -304,6 +312,7 @@ __device__ __forceinline__ void item_gemv(const MoeArgs& a, const Run& run, cons
         default: NQ_LOOP(true, 0); break;
     }
 #undef NQ_LOOP
+#undef NQ_LOOP1
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -346,11 +355,11 @@ __global__ void __launch_bounds__(256, NQ_GEMV_MINBLOCKS) gemv_kernel(MoeArgs a)
         const int ntok = run.ntok, level = run.level;
         const int64_t* row = a.table + (int64_t)run.expert * kTableWidth;
         const ProjPlanes P = planes_from_row(row, DOWN);
-        const int rc = (int)row[10 + DOWN], nm = DOWN ? a.nm_dn : a.nm_gu;
+        const int rc = (int)row[10 + DOWN], nm = DOWN ? a.nm_dn : a.nm_gu, bk = (int)(row[19] >> (8 * DOWN)) & 0xFF;
         const int row0 = DOWN ? grp * 128 : up * a.I + grp * 128, strip = row0 / 16 + warp;
         const int c0 = ks * (C / KS), c1 = c0 + C / KS;
 
-        item_gemv<DOWN, 1>(a, run, P, level, rc, nm, strip, C, NS, c0, c1, up, ks, part, N, S, smem_ring + warp * (kDepth * kStageBytes));
+        item_gemv<DOWN, 1>(a, run, P, level, rc, bk, nm, strip, C, NS, c0, c1, up, ks, part, N, S, smem_ring + warp * (kDepth * kStageBytes));
         int* cnt = DOWN ? a.cnt_d + grp : a.cnt_gu + r * (a.I / 128) + grp;
         const int expect = DOWN ? nruns * KS : 2 * KS;
         __threadfence();

@@ -43,9 +43,9 @@ __global__ void __launch_bounds__(256) pf_decode_kernel(const int64_t* __restric
         return;
     }
     const ProjPlanes P = planes_from_row(row, down);
-    const int nm = down ? nm_dn : nm_gu, rc = (int)row[10 + down];
+    const int nm = down ? nm_dn : nm_gu, rc = (int)row[10 + down], bk = (int)(row[19] >> (8 * down)) & 0xFF;
     const UnitRef u = locate_unit(P, strip, ch, C, NS, nm, level);
-    decode_unit_dispatch(P, u, rc, lane, TileSink{tile, lane >> 2, lane & 3});
+    decode_unit_dispatch(P, u, rc, bk, lane, TileSink{tile, lane >> 2, lane & 3});
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 8; ++j)

@@ -273,7 +273,7 @@ struct UnitSink
 
 // One decode warp, one item: its strip over the chunks c = GROUP, GROUP + 2, ... (the other group of 8 warps takes the
 // other parity), i.e. k-blocks 4 i + 2 GROUP and + 1.  it_base = k-blocks of earlier items.  false = aborted.
-template <bool REFINED, int RC, class Mid>
+template <bool REFINED, int RC, int BK, class Mid>
 __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int C, int NS, int nm, int lane, int group,
                                              uint32_t tmem_a, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
 {
@@ -302,7 +302,7 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
         }
     }
     auto issue = [&](int ch, uint8_t* st) {
-        cp_async16(st + lane * 16, (const uint8_t*)(P.base + (unit0 + ch) * 32 + lane));
+        copy_base<BK>(st, P.base, (unit0 + ch) * 32 + lane, (size_t)NS * C * 32, lane);
         if constexpr (REFINED)
             if ((fl >> ch) & 1ull) copy_record<RC>(st + 512, P.p4, res_unit(ch) * 32 + lane, res_nrec, lane);
     };
@@ -324,8 +324,8 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
         slot_in = slot_in + 1 == kPfRingDepth ? 0 : slot_in + 1;
         const uint32_t vb = __shfl_sync(0xffffffffu, var_b, i);
         const uint32_t sign2 = ((vb >> (lane >> 2)) & 1u) * 0x80008000u;
-        const uint4 b = *(const uint4*)(st + lane * 16);
-        uint32_t wb[6] = {b.x, b.y, b.z, b.w, 0u, 0u};
+        uint32_t wb[Pattern<BK>::kWords + 2];
+        read_base<BK>(wb, st, (unit0 + ch) * 32 + lane, lane);
         const UnitSink sink{tmem_a, sh, it_base + 2 * (uint32_t)ch, lane, &ok};
         bool refined = false;
         if constexpr (REFINED) refined = (fl >> ch) & 1ull;
@@ -348,10 +348,10 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
             k.mrep = __byte_perm(mb, 0u, 0x0000); k.nrep = __byte_perm(mb, 0u, 0x1111);
             uint32_t wr[Pattern<RC>::kWords + 2];
             read_record<RC>(wr, st + 512, res_unit(ch) * 32 + lane, lane);
-            decode_words<true, RC>(wb, wr, k, lane, sink);
+            decode_words<true, RC, BK>(wb, wr, k, lane, sink);
         }
         else
-            decode_words<false, 0>(wb, nullptr, consts_level2(sign2), lane, sink);
+            decode_words<false, 0, BK>(wb, nullptr, consts_level2(sign2), lane, sink);
 #endif
         if (i == 0) mid();      // the previous item's epilogue, once this item's first tiles are on their way
     }
@@ -360,10 +360,17 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
 }
 
 template <class Mid>
-__device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int rc, int strip, int C, int NS, int nm, int lane, int group,
+__device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int rc, int bk, int strip, int C, int NS, int nm, int lane, int group,
                                             uint32_t tmem_a, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
 {
-#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV>(P, strip, C, NS, nm, lane, group, tmem_a, ring, sh, it_base, mid)
+#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV, 0>(P, strip, C, NS, nm, lane, group, tmem_a, ring, sh, it_base, mid)
+#define NQ_RUN1(REF, RCV) return decode_strip<REF, RCV, 1>(P, strip, C, NS, nm, lane, group, tmem_a, ring, sh, it_base, mid)
+    if (bk == 1)        // 112-bit base records, with the residual codes they ship with
+    {
+        if (level < 4) NQ_RUN1(false, 0);
+        if (rc == 9) NQ_RUN1(true, 9);
+        NQ_RUN1(true, 3);
+    }
     if (level < 4) NQ_RUN(false, 0);
     switch (rc)
     {
@@ -379,6 +386,7 @@ __device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int 
         default: NQ_RUN(true, 0);
     }
 #undef NQ_RUN
+#undef NQ_RUN1
 }
 
 // grid = resident CTAs (one per SM), 576 threads
@@ -514,13 +522,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             const int64_t* row = a.table + (int64_t)ps.expert * kTableWidth;
             const int level = (int)row[0];
             const ProjPlanes P = planes_from_row(row, a.down);
-            const int rc = (int)row[10 + a.down], nm = a.down ? a.nm_dn : a.nm_gu;
+            const int rc = (int)row[10 + a.down], nm = a.down ? a.nm_dn : a.nm_gu, bk = (int)(row[19] >> (8 * a.down)) & 0xFF;
             uint8_t* ring = rings + dw * kPfRingDepth * kStageBytes;
             // group `half` of 8 warps decodes the chunks of that parity: k-blocks 4 i + 2 half and + 1.  The epilogue
             // of the previous item runs after this item's first unit is decoded: the MMAs of the previous item's last
             // k-blocks finish meanwhile, and the tensor pipe finds tiles waiting when the accumulator is free again.
             auto mid = [&]() { if (have_prev) { epilogue(prev, prev_wg, prev_up, nitem - 1); have_prev = false; } };
-            const bool ok = decode_item(P, level, rc, wg * 8 + sidx, C, NS, nm, lane, half, tmem_a, ring, sh, it, mid);
+            const bool ok = decode_item(P, level, rc, bk, wg * 8 + sidx, C, NS, nm, lane, half, tmem_a, ring, sh, it, mid);
             it += nkb;
             mid();                                   // (an item of fewer than two chunks: its second warp group decodes nothing)
             if (ok) { prev = ps; prev_wg = wg; prev_up = up; have_prev = true; }

@@ -84,4 +84,27 @@ __device__ __forceinline__ void read_record(uint32_t* w, const uint8_t* st, size
     }
 }
 
+// base records of a unit in the first 512 bytes of a stage: one 16-byte copy per lane for base code 0, the sub-array
+// pieces (same slot layout as a residual record) for the others
+template <int BK>
+__device__ __forceinline__ void copy_base(uint8_t* st, const uint4* __restrict__ base, size_t rec, size_t nrec, int lane)
+{
+    if constexpr (BK == 0) cp_async16(st + lane * 16, (const uint8_t*)(base + rec));
+    else
+    {
+        static_assert(ResidualSlots<BK>::end <= 512, "base record does not fit the base part of a stage");
+        copy_record<BK>(st, (const uint8_t*)base, rec, nrec, lane);
+    }
+}
+template <int BK>
+__device__ __forceinline__ void read_base(uint32_t* wb, const uint8_t* st, size_t rec, int lane)
+{
+    if constexpr (BK == 0)
+    {
+        const uint4 b = *(const uint4*)(st + lane * 16);
+        wb[0] = b.x; wb[1] = b.y; wb[2] = b.z; wb[3] = b.w;
+    }
+    else read_record<BK>(wb, st, rec, lane);
+}
+
 }  // namespace nq

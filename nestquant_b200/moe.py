@@ -127,7 +127,8 @@ def all_MbN():
 class Proj:
     """Seeded random packed planes of one N x K projection of one expert.
 
-    base  int32 [S*C*32*4]   one 128-bit record per lane
+    base  int32 [S*C*32*4]   one 128-bit record per lane (base code 0); for other base codes the sub-array layout at
+                             rbits(bk) bits per record
     p4    int32 view of the residual plane in the sub-array layout (+ 4 B pad when the record has a bit tail)
     d4    int32 [S*R]        block word Mb | N << 8 per refined unit
     var   uint8 [S*C] or None: bit g negates ring g.   flags int64 [S] or None (mask mode, nm flagged chunks/strip)
@@ -136,14 +137,19 @@ class Proj:
     """
 
     def __init__(s, N, K, gen, nm=None, rk=0, mbn="rand", var=False, bk=0):
-        if bk != 0:
-            raise NotImplementedError("only the 128-bit ring base (base code 0) is built into the kernels")
         z = proj_sizes(N, K, nm, rk, bk)
         s.z, s.N, s.K, s.rk, s.bk = z, N, K, rk, bk
         S, C = z["S"], z["C"]
         R = C if nm is None else nm
         dev = gen.device
-        s.base = torch.randint(-2**31, 2**31 - 1, (S * C * 32 * 4,), generator=gen, dtype=torch.int32, device=dev)
+        if bk == 0:
+            s.base = torch.randint(-2**31, 2**31 - 1, (S * C * 32 * 4,), generator=gen, dtype=torch.int32, device=dev)
+        else:           # pattern-rate base: rbits(bk) bits per record in the sub-array layout (sm120/NQ_RES_V2.md:36-41)
+            bb = rbits(bk)
+            wb = torch.randint(0, 2**32, (S * C * 32, (bb + 31) // 32), generator=gen, dtype=torch.int64, device=dev)
+            if bb % 32:
+                wb[:, -1] &= (1 << (bb % 32)) - 1
+            s.base = pack_words(wb.cpu(), bb).to(dev)
         nb = z["p4"]
         raw = torch.randint(0, 256, ((nb + 3) // 4 * 4,), generator=gen, dtype=torch.uint8, device=dev)
         if rbits(rk) % 16:
@@ -196,11 +202,11 @@ class Expert:
     output scales are +-1 (sv=None, the reference's synthetic default) or |N(0, sv)|."""
 
     def __init__(s, H, I, seed, nm_gu=None, nm_dn=None, dev="cuda", rk_gu=0, rk_dn=0, mbn="rand", var=False, sv=None,
-                 gen_device="cpu"):
+                 gen_device="cpu", bk_gu=0, bk_dn=0):
         gen = torch.Generator(device=gen_device).manual_seed(seed)
-        s.gu = Proj(2 * I, H, gen, nm_gu, rk_gu, mbn, var).to(dev)
+        s.gu = Proj(2 * I, H, gen, nm_gu, rk_gu, mbn, var, bk_gu).to(dev)
         mbn_dn = mbn if mbn == "rand" else ("exh", mbn[1] + (2 * I // 16) * (H // 128))
-        s.dn = Proj(H, I, gen, nm_dn, rk_dn, mbn_dn, var).to(dev)
+        s.dn = Proj(H, I, gen, nm_dn, rk_dn, mbn_dn, var, bk_dn).to(dev)
         sg = (torch.randint(0, 2, (3 * H + 3 * I,), generator=gen, device=gen_device) * 2 - 1).float()
         if sv is not None:
             mag = (torch.randn(3 * H + 3 * I, generator=gen, device=gen_device) * sv).abs()
@@ -292,6 +298,9 @@ class MoELayer:
         if bks != (0, 0):
             bkm = s.M.bk_codes()
             assert bkm[0] >> bks[0] & 1 and bkm[1] >> bks[1] & 1, f"base K code gu {bks[0]} / dn {bks[1]} not compiled (bk_codes {bkm})"
+            if level == 4:      # base code 1 is built with the residual codes it ships with
+                for p, name in ((ex.gu, "gu"), (ex.dn, "dn")):
+                    assert base_code(p) == 0 or p.rk in (3, 9), f"{name}: base K code {base_code(p)} is built with residual codes 3 and 9, not {p.rk}"
         if level == 4:
             rkm = s.M.rk_codes()
             assert rkm[0] >> ex.gu.rk & 1 and rkm[1] >> ex.dn.rk & 1, f"residual K code gu {ex.gu.rk} / dn {ex.dn.rk} not compiled (rk_codes {rkm})"

@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_format_queries_need_no_gpu():
     from nestquant_b200 import ext, moe
-    assert ext.rk_codes() == [1023, 1023] and ext.bk_codes() == [1, 1]
+    assert ext.rk_codes() == [1023, 1023] and ext.bk_codes() == [3, 3]
     lib = __import__("nestquant_b200.capi", fromlist=["lib"]).lib()
     for c in range(10):
         assert lib.nq_plane_bytes(12288 * 32, c) == moe.proj_sizes(4096, 6144, None, c)["p4"]

@@ -27,6 +27,7 @@ def _decode_gu(planes, level, nm):
     for i, t in enumerate(keep[:4]):
         row[0, 1 + i] = 0 if t is None else t.data_ptr()
     row[0, 10] = planes.rk
+    row[0, 19] = planes.bk
     row[0, 12] = 0 if keep[4] is None else keep[4].data_ptr()
     table = row.cuda()
     W = torch.full((planes.N, planes.K), float("nan"), dtype=torch.float16, device="cuda")
@@ -40,13 +41,11 @@ def test_golden_projections_bit_exact():
     n = 0
     for i in range(int(z["ncases"][0])):
         p = proj_from(z, f"case{i}.")
-        if p.bk != 0:
-            continue                      # base window code 1 is not built into the kernels
         for level in (2, 4):
             got = _decode_gu(p, level, p.nm)
             assert same_fp16_bits(got, z[f"case{i}.W{level}"]) == 0, (i, level)
             n += 1
-    assert n >= 28
+    assert n >= 32
 
 
 @pytest.mark.parametrize("rk", range(10))
@@ -55,6 +54,20 @@ def test_random_projection_vs_oracle(rk):
     gen = torch.Generator().manual_seed(40 + rk)
     for nm in (None, 3):
         p = moe.Proj(256, 1024, gen, nm=nm, rk=rk, mbn=("exh", rk * 3000), var=rk % 2 == 0)
+        po = proj_to_oracle(p)
+        for level in (2, 4):
+            got = _decode_gu(po, level, nm or 0)
+            assert same_fp16_bits(got, O.decode_proj(po, level)) == 0, (rk, nm, level)
+
+
+@pytest.mark.parametrize("rk", (3, 9))
+def test_pattern_rate_base_vs_oracle(rk):
+    """base window code 1 (1.75 bits per weight, 112-bit records in the sub-array layout) with the residual codes it ships
+    with (sm120/NQ_RES_V2.md), dense and mask mode"""
+    from nestquant_b200 import moe
+    gen = torch.Generator().manual_seed(70 + rk)
+    for nm in (None, 2):
+        p = moe.Proj(256, 1024, gen, nm=nm, rk=rk, mbn=("exh", rk * 2500), var=True, bk=1)
         po = proj_to_oracle(p)
         for level in (2, 4):
             got = _decode_gu(po, level, nm or 0)

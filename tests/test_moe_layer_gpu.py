@@ -110,6 +110,41 @@ def test_mixed_levels_vs_oracle(H, I):
             _check(L, exs_o, levels, x, sel, rw, (H, I, B, mode))
 
 
+def test_pattern_rate_base_layer_decode_and_prefill():
+    """Experts with the 1.75-bit base (base code 1) and the residual codes of that build (3 for gate|up, 9 for down) beside
+    ordinary ones, levels 2 and 4, one in mask mode: decode path and fused prefill against the oracle."""
+    from nestquant_b200 import moe
+    H, I, NE, topk = 768, 512, 6, 3
+    nmg, nmd = H // 128 // 2, I // 128 // 2
+    exs = [moe.Expert(H, I, seed=600 + i, nm_gu=nmg if i == 3 else None, nm_dn=nmd if i == 3 else None, rk_gu=3 if i < 4 else 0,
+                      rk_dn=9 if i < 4 else 7, var=True, sv=0.02, bk_gu=1 if i < 4 else 0, bk_dn=1 if i < 4 else 0) for i in range(NE)]
+    exs_o = [expert_to_oracle(e) for e in exs]
+    levels = [4, 2, 4, 4, 4, 2]
+    L = moe.MoELayer(NE, H, I, nmg, nmd, Bmax=8, topk=topk)
+    for e in range(NE):
+        L.set(e, exs[e], levels[e])
+    rng = random.Random(5)
+    gen = torch.Generator().manual_seed(6)
+    for B in (1, 4, 8):
+        sel, rw = _routing(B, NE, topk, rng)
+        x = torch.randn(B, H, generator=gen).bfloat16().half()
+        _check(L, exs_o, levels, x, sel, rw, ("bk1", B))
+    T = 150
+    sel, rw = _routing(T, NE, topk, rng)
+    x = torch.randn(T, H, generator=gen).bfloat16().half()
+    ref = O.moe_ref(exs_o, levels, x.numpy(), sel.numpy(), rw.numpy())
+    y = L.prefill(x.cuda(), sel.cuda(), rw.cuda())
+    y_lib = L.prefill(x.cuda(), sel.cuda(), rw.cuda(), fused=False)
+    torch.cuda.synchronize()
+    for got in (y, y_lib):
+        ma, rl = layer_errors(got.cpu().numpy(), ref)
+        assert ma <= MAX_ABS_TOL and rl <= 5e-4, (ma, rl)
+    bad = moe.Expert(H, I, seed=1, rk_gu=0, rk_dn=7, bk_gu=1, bk_dn=1)
+    with pytest.raises(AssertionError):
+        L.set(0, bad, 4)                      # base code 1 is built with residual codes 3 and 9 only
+    L.set(0, bad, 2)                          # at level 2 the residual code does not matter
+
+
 def test_glm_shape_one_and_four_tokens():
     from nestquant_b200 import moe
     H, I, NE, topk = 6144, 2048, 10, 8
