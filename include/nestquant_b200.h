@@ -185,6 +185,14 @@ int nq_moe_forward_static(const void* x, const int64_t* sel, const void* rw, con
                           int B, int topk, int E, int H, int I, int nm_gu, int nm_dn, int ks_gu, int ks_dn,
                           int32_t* hits, void* stream);
 
+/* Decode salience export: acc[e] += sum over the picks (t, k) with sel[t][k] == e and rw[t][k] != 0 of
+ * (rsf * rw[t][k])^2 * sum_i x[t][i]^2; every touched entry is also stored to host[e] (host-mapped fp64 [E], may be NULL).
+ * x fp16 or bf16 [B][row_stride >= H] (the layer input), rw fp16 [B][topk], sel int64 [B][topk], acc fp64 [E] on the
+ * device.  One launch, no host sync; calls on one layer must be stream-ordered.
+ * Replaces sal() (sm120/nqsal.cu:18-77), with this library's decode limits (32 tokens, 256 picks). */
+int nq_salience(const void* x, int x_is_bf16, int64_t row_stride, const void* rw, const int64_t* sel, int B, int H, int topk,
+                int E, float rsf, double* acc, double* host, void* stream);
+
 /* ---- promotion engine (host side) -------------------------------------------------------------------------------
  * One engine per GPU process, reading that process's record file (fixed-size records, see nestquant_b200/p4rec.py).
  * Replaces the torch-extension class Engine of streaming/nqstream.cu:46-283 (upgrade / post / poll / cancel /

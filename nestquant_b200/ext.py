@@ -183,3 +183,17 @@ def moe_forward_static(x, sel, rw, table, out, I, nm_gu, nm_dn, ks_gu, ks_dn, hi
     check(lib().nq_moe_forward_static(ptr(x), ptr(sel), ptr(rw), ptr(table), ptr(out), x.shape[0], sel.shape[1], table.shape[0],
                                       x.shape[1], I, nm_gu, nm_dn, ks_gu, ks_dn, hits_ptr or None, current_stream()),
           "moe_forward_static")
+
+
+def sal(x, w, ids, rsf, acc, host_ptr=0):
+    """salience export of one decode call (the reference's nqsal.sal): acc[e] += (rsf * w)^2 * |x[t]|^2 over the picks of e.
+    x fp16 / bf16 [T,H] (rows may be strided), w fp16 [T,topk], ids int64 [T,topk], acc fp64 [E] (device),
+    host_ptr: raw address of a host-mapped fp64 [E] mirror, or 0"""
+    if x.dtype not in (torch.float16, torch.bfloat16) or x.dim() != 2 or x.stride(1) != 1:
+        raise NestQuantError("sal: x must be fp16 or bf16 [T, H] with unit column stride")
+    _need(w, torch.float16, "w"); _need(ids, torch.int64, "ids"); _need(acc, torch.float64, "acc")
+    T, H = x.shape
+    if w.numel() != ids.numel() or (T and ids.numel() % T):
+        raise NestQuantError("sal sizes")
+    check(lib().nq_salience(ptr(x), int(x.dtype == torch.bfloat16), x.stride(0) if T else H, ptr(w), ptr(ids), T, H,
+                            ids.shape[1], acc.numel(), float(rsf), ptr(acc), host_ptr or None, current_stream()), "sal")

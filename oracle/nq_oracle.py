@@ -172,6 +172,21 @@ def moe_ref(experts, levels, x16: np.ndarray, sel: np.ndarray, rw16: np.ndarray,
     return out
 
 
+def salience_ref(x, rw16, sel, rsf, E):
+    """salience added by one decode call (sm120/nqsal.cu:3-5): sal[e] = sum over picks (t, k) of e with weight != 0 of
+    (rsf * w)^2 * sum_i x[t, i]^2; x [T, H] float, rw16 fp16 [T, topk], sel int [T, topk] -> float64 [E].
+    The weight product follows the kernel's fp32 order; the norm is summed in float64 (the kernel sums fp32 partials)."""
+    xn = (np.asarray(x, np.float64) ** 2).sum(1)
+    out = np.zeros(E, np.float64)
+    for t in range(sel.shape[0]):
+        for k in range(sel.shape[1]):
+            w = np.float32(rw16[t, k])
+            if w != 0 and 0 <= sel[t, k] < E:
+                w = np.float32(w * np.float32(rsf))
+                out[int(sel[t, k])] += float(np.float32(w * w)) * xn[t]
+    return out
+
+
 # ------------------------------------------------------------------ numpy second opinion (one unit)
 def _step_off(p, KA, MASK):
     per = np.array([sum(KA + ((MASK >> i) & 1) for i in range(r)) for r in range(16)])
