@@ -193,6 +193,14 @@ int nq_moe_forward_static(const void* x, const int64_t* sel, const void* rw, con
 int nq_salience(const void* x, int x_is_bf16, int64_t row_stride, const void* rw, const int64_t* sel, int B, int H, int topk,
                 int E, float rsf, double* acc, double* host, void* stream);
 
+/* Expert-parallel combine over peer memory: out[t] (fp32 [T][H]) = sum over the ranks r = 0 .. world - 1, in that order,
+ * of row rows[r * T + t] (int32, -1 = none) of peer_parts[r] (fp32 [.][H], device addresses of every rank's partial-row
+ * buffer as seen from this GPU: symmetric memory / peer mappings; host array of `world` pointers).  Plain peer loads.
+ * The caller makes the peers' rows complete before the call and keeps them unchanged until it has run (barriers).
+ * No counterpart in the reference (its serving path is tensor-parallel); it takes the place of the combine all-to-all
+ * plus the indexed add of an expert-parallel prefill. */
+int nq_ep_combine(float* out, const void* const* peer_parts, const int32_t* rows, int T, int H, int world, void* stream);
+
 /* ---- promotion engine (host side) -------------------------------------------------------------------------------
  * One engine per GPU process, reading that process's record file (fixed-size records, see nestquant_b200/p4rec.py).
  * Replaces the torch-extension class Engine of streaming/nqstream.cu:46-283 (upgrade / post / poll / cancel /

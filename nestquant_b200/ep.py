@@ -9,8 +9,11 @@ Two exchange patterns, both over torch.distributed (NCCL on GPUs, gloo in the CP
                         reduce-scatter (sm120/eval/eval_reg.py:137-142,181); latency-bound, tiny messages.
   prefill(x, sel, rw)   tokens sharded (each rank owns T_r tokens): dispatch = all-to-all of each token row to every
                         rank that owns one of its picked experts (once per destination rank, not once per pick), with
-                        its picks masked to that rank; local prefill on the received rows; combine = all-to-all of the
-                        fp32 partial rows back; the owner adds the partials in rank order (deterministic).
+                        its picks masked to that rank; local prefill on the received rows; combine = the owner adds
+                        the partial rows in rank order (deterministic).  On NVLink-connected GPUs the partial rows stay
+                        where they were computed, in a symmetric-memory buffer, and the owner's combine kernel
+                        (nq_ep_combine) reads them from the peers directly; otherwise (gloo, no peer access, more rows
+                        than the buffer holds) they come back by an all-to-all and an indexed add.
 
 The local layer is any object with .E, .H, __call__(x, sel, rw) and .prefill(x, sel, rw) - nestquant_b200.moe.MoELayer on a
 GPU; the CPU tests plug in a stand-in to check the exchange logic without a device.
@@ -50,21 +53,48 @@ def _all_to_all(out_splits, inp, in_splits, group):
 
 
 def _exchange_counts(counts, group):
-    """counts[d] = rows this rank sends to rank d  ->  rows it receives from each rank"""
-    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    """counts[d] = rows this rank sends to rank d  ->  the whole matrix m[src][dst] as nested lists (host)"""
+    world = dist.get_world_size(group)
     allc = [torch.empty_like(counts) for _ in range(world)]
     dist.all_gather(allc, counts, group=group)
-    return [int(allc[src][rank]) for src in range(world)]
+    return torch.stack(allc).cpu().tolist()
+
+
+class _PeerRows:
+    """symmetric-memory buffer [rows, H] fp32 per rank for the partial rows of the prefill, with every rank's address"""
+
+    def __init__(s, rows, H, dev, group):
+        import torch.distributed._symmetric_memory as symm
+        s.buf = symm.empty(rows, H, dtype=torch.float32, device=dev)
+        s.hdl = symm.rendezvous(s.buf, group if group is not None else dist.group.WORLD)
+        s.rows = rows
+        s.ptrs = [int(p) for p in s.hdl.buffer_ptrs]
+
+    def barrier(s):
+        s.hdl.barrier()
 
 
 class EPLayer:
-    def __init__(s, local_layer, rank=None, world=None, group=None):
+    def __init__(s, local_layer, rank=None, world=None, group=None, peer_rows=0):
+        """peer_rows > 0: keep up to that many partial rows per rank in symmetric memory and combine over peer loads
+        (NCCL groups on peer-connected GPUs only; silently off where symmetric memory cannot be set up)."""
         s.L, s.group = local_layer, group
         s.rank = dist.get_rank(group) if rank is None else rank
         s.world = dist.get_world_size(group) if world is None else world
         s.E, s.H = local_layer.E, local_layer.H
         s.per = (s.E + s.world - 1) // s.world
         s.last_stats = {}
+        s.peer = None
+        if peer_rows > 0 and s.world > 1 and s.world <= 8 and _has_alltoall(group):
+            ok = torch.ones(1, dtype=torch.int32, device=local_layer.table.device)
+            try:
+                s.peer = _PeerRows(peer_rows, s.H, local_layer.table.device, group)
+            except Exception as e:                      # no peer access / no symmetric memory on this system
+                s.peer_error = repr(e)
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)       # all ranks take the same path
+            if int(ok) == 0:
+                s.peer = None
 
     # ---- 1..32 replicated tokens
     def decode(s, x, sel, rw, out=None):
@@ -90,14 +120,36 @@ class EPLayer:
             send_sel.append(sel[rows])
             send_rw.append(torch.where(mine[rows], rw[rows], torch.zeros_like(rw[rows])))   # picks of other ranks: weight 0
         in_splits = [int(r.numel()) for r in idx]
-        out_splits = _exchange_counts(torch.tensor(in_splits, dtype=torch.int64, device=dev), s.group)   # host sync: split sizes
+        m = _exchange_counts(torch.tensor(in_splits, dtype=torch.int64, device=dev), s.group)            # host sync: split sizes
+        out_splits = [int(m[src][s.rank]) for src in range(s.world)]
         xr = _all_to_all(out_splits, torch.cat(send_x), in_splits, s.group)
         selr = _all_to_all(out_splits, torch.cat(send_sel), in_splits, s.group)
         rwr = _all_to_all(out_splits, torch.cat(send_rw), in_splits, s.group)
         s.last_stats = dict(sent_rows=sum(in_splits), recv_rows=sum(out_splits), dispatch_bytes=sum(in_splits) * s.H * 2,
                             combine_bytes=sum(out_splits) * s.H * 4)
+        nrecv = sum(out_splits)
+        if s.peer is not None and max(sum(int(m[src][d]) for src in range(s.world)) for d in range(s.world)) <= s.peer.rows:
+            # partial rows stay in this rank's symmetric buffer; every owner reads what it needs from its peers
+            from .capi import check, lib
+            import ctypes as C
+            if nrecv:
+                s.L.prefill(xr, selr, rwr, out=s.peer.buf[:nrecv])
+            rows = torch.full((s.world, T), -1, dtype=torch.int32, device=dev)
+            for d in range(s.world):
+                if in_splits[d]:                                                   # my rows sit after those of the ranks before me
+                    first = sum(int(m[src][d]) for src in range(s.rank))
+                    rows[d, idx[d]] = torch.arange(first, first + in_splits[d], dtype=torch.int32, device=dev)
+            out = torch.empty(T, s.H, dtype=torch.float32, device=dev)
+            s.peer.barrier()                                                       # every rank's partial rows are complete
+            ptrs = (C.c_void_p * s.world)(*s.peer.ptrs)
+            check(lib().nq_ep_combine(out.data_ptr(), ptrs, rows.data_ptr(), T, s.H, s.world, torch.cuda.current_stream(dev).cuda_stream),
+                  "ep_combine")
+            s.peer.barrier()                                                       # buffers may be overwritten from here on
+            s.last_stats["combine"] = "peer loads"
+            return out
         part = s.L.prefill(xr, selr, rwr) if xr.shape[0] else torch.zeros(0, s.H, dtype=torch.float32, device=dev)
         back = _all_to_all(in_splits, part, out_splits, s.group)                   # partial rows return to their owners
+        s.last_stats["combine"] = "all-to-all"
         out = torch.zeros(T, s.H, dtype=torch.float32, device=dev)
         o = 0
         for d in range(s.world):                                                   # fixed rank order: repeatable sums

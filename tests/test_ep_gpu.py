@@ -1,0 +1,70 @@
+"""Expert-parallel layer on 2 GPUs (skipped on a single-GPU box): the prefill whose combine reads the partial rows from
+the peers' symmetric-memory buffers (nq_ep_combine) must equal, bit for bit, the all-to-all + indexed-add path, and both
+must match a single-GPU layer holding every expert; decode = replicated tokens + all-reduce."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    try:
+        from nestquant_b200 import moe
+        from nestquant_b200.ep import EPLayer, owned_experts
+        from tests.util import layer_errors
+        H, I, NE, topk, T = 1024, 512, 8, 3, 192
+        exs = [moe.Expert(H, I, seed=700 + i, rk_gu=0, rk_dn=7, var=True, sv=0.02, dev=dev) for i in range(NE)]
+        levels = [4, 2, 4, 4, 2, 4, 4, 2]
+        mine = set(owned_experts(NE, world, rank))
+        full = moe.MoELayer(NE, H, I, Bmax=4, topk=topk, dev=dev)
+        part = moe.MoELayer(NE, H, I, Bmax=4, topk=topk, dev=dev, share=1.0 / world)
+        for e in range(NE):
+            full.set(e, exs[e], levels[e])
+            part.set(e, exs[e], levels[e] if e in mine else 0)
+        g = torch.Generator().manual_seed(9)                      # same inputs on every rank; each rank owns a slice of the tokens
+        x = torch.randn(world * T, H, generator=g).bfloat16().half()
+        sel = torch.stack([torch.randperm(NE, generator=g)[:topk] for _ in range(world * T)])
+        rw = torch.softmax(torch.randn(world * T, topk, generator=g), 1).half()
+        sl = slice(rank * T, (rank + 1) * T)
+        xr, selr, rwr = x[sl].to(dev), sel[sl].to(dev), rw[sl].to(dev)
+        ref = full.prefill(xr, selr, rwr)
+        ep_a2a = EPLayer(part, rank, world)
+        ep_peer = EPLayer(part, rank, world, peer_rows=world * T)
+        y_a2a = ep_a2a.prefill(xr, selr, rwr)
+        y_peer = ep_peer.prefill(xr, selr, rwr)
+        y_peer2 = ep_peer.prefill(xr, selr, rwr)
+        torch.cuda.synchronize()
+        res = dict(peer_on=ep_peer.peer is not None, combine=ep_peer.last_stats.get("combine"),
+                   same=bool(torch.equal(y_a2a, y_peer)) and bool(torch.equal(y_peer, y_peer2)),
+                   err=layer_errors(y_peer.cpu().numpy(), ref.cpu().numpy())[1])
+        xd, seld, rwd = x[:3].to(dev), sel[:3].to(dev), rw[:3].to(dev)
+        yd = ep_a2a.decode(xd, seld, rwd).clone()
+        res["decode_err"] = layer_errors(yd.cpu().numpy(), full(xd, seld, rwd).cpu().numpy())[1]
+        q.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_prefill_combine_over_peer_memory():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29600 + os.getpid() % 300
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0, p.exitcode
+    out = dict(q.get(timeout=10) for _ in range(2))
+    for rank, r in out.items():
+        assert r["peer_on"] and r["combine"] == "peer loads", (rank, r)
+        assert r["same"] and r["err"] <= 1e-4 and r["decode_err"] <= 1e-4, (rank, r)
