@@ -193,6 +193,15 @@ int nq_moe_forward_static(const void* x, const int64_t* sel, const void* rw, con
 int nq_salience(const void* x, int x_is_bf16, int64_t row_stride, const void* rw, const int64_t* sel, int B, int H, int topk,
                 int E, float rsf, double* acc, double* host, void* stream);
 
+/* Expert-parallel dispatch over peer memory: for every global token t (rank t / tokens_per_rank owns it) that has a pick
+ * with a non-zero weight among this rank's experts (expert / experts_per_rank == rank), copy its fp16 input row from the
+ * owner's buffer peer_x[owner] ([tokens_per_rank][H], device addresses as seen from this GPU) into xstage[t]
+ * ([world * tokens_per_rank][H]); other rows of xstage are left untouched.  sel int64 / rw fp16: the picks of ALL tokens
+ * ([world * tokens_per_rank][topk], e.g. from an all-gather).  Plain peer loads; the caller's barrier makes the peers'
+ * rows complete first.  No counterpart in the reference; it takes the place of the dispatch all-to-all. */
+int nq_ep_gather(void* xstage, const void* const* peer_x, const int64_t* sel, const void* rw, int tokens_per_rank, int topk, int H,
+                 int world, int rank, int experts_per_rank, void* stream);
+
 /* Expert-parallel combine over peer memory: out[t] (fp32 [T][H]) = sum over the ranks r = 0 .. world - 1, in that order,
  * of row rows[r * T + t] (int32, -1 = none) of peer_parts[r] (fp32 [.][H], device addresses of every rank's partial-row
  * buffer as seen from this GPU: symmetric memory / peer mappings; host array of `world` pointers).  Plain peer loads.

@@ -1,11 +1,19 @@
-// Expert-parallel combine over peer memory: out[t] = sum over the ranks r, in rank order, of the partial row rank r
-// computed for token t, read straight from rank r's buffer over NVLink (plain peer loads).
+// Expert-parallel exchange over peer memory (plain peer loads over NVLink, no collective on the data path).
+//
+// Dispatch: every rank keeps its tokens' input rows in a symmetric buffer; nq_ep_gather copies, into a local staging
+// matrix indexed by global token, the rows of exactly those tokens that picked one of this rank's experts (each row
+// crosses NVLink once per destination rank, as in an all-to-all, but pulled by the consumer and without any size
+// exchange on the host).
+// Combine: out[t] = sum over the ranks r, in rank order, of the partial row rank r computed for token t, read straight
+// from rank r's buffer.
 //
 // This is the return leg of the expert-parallel prefill (the reference names the exchange, sm120/eval/eval_reg.py:137-142;
 // its serving path is tensor-parallel and has no counterpart kernel): instead of an all-to-all of the partial rows into a
 // receive buffer followed by an indexed add, the owner of a token gathers and sums its partial rows in one pass.  The
 // buffers are symmetric-memory allocations whose peer addresses the host passes in; the host brackets the call with the
 // barriers that make the peers' rows complete before and keep them untouched during the reads.
+#include <cuda_fp16.h>
+
 #include "nq_common.cuh"
 
 namespace nq {
@@ -35,7 +43,43 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(float* __restrict__ out
     }
 }
 
+// one CTA per global token: copy its row from the owner's buffer if any of its picks with a weight belongs to `rank`
+__global__ void __launch_bounds__(128) ep_gather_kernel(__half* __restrict__ xstage, EpPeers peers, const int64_t* __restrict__ sel,
+                                                        const __half* __restrict__ rw, int tokens_per_rank, int topk, int H, int rank, int per)
+{
+    const int t = blockIdx.x;
+    bool need = false;
+    for (int k = 0; k < topk; ++k)
+    {
+        const int64_t e = sel[(size_t)t * topk + k];
+        need |= e >= 0 && e / per == rank && __half2float(rw[(size_t)t * topk + k]) != 0.f;
+    }
+    if (!need) return;
+    const int owner = t / tokens_per_rank;
+    const uint4* src = (const uint4*)((const __half*)peers.part[owner] + (size_t)(t - owner * tokens_per_rank) * H);
+    uint4* dst = (uint4*)(xstage + (size_t)t * H);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
 }  // namespace nq
+
+extern "C" int nq_ep_gather(void* xstage, const void* const* peer_x, const int64_t* sel, const void* rw, int tokens_per_rank, int topk, int H,
+                            int world, int rank, int experts_per_rank, void* stream)
+{
+    NQ_REQUIRE(tokens_per_rank >= 0 && topk >= 1 && H > 0 && H % 8 == 0 && world >= 1 && world <= nq::kEpMaxRanks && rank >= 0 && rank < world &&
+               experts_per_rank >= 1, "nq_ep_gather: bad shape (tokens %d, topk %d, H %d, world %d, rank %d)", tokens_per_rank, topk, H, world, rank);
+    if (tokens_per_rank == 0) return NQ_OK;
+    NQ_REQUIRE(xstage && peer_x && sel && rw && nq::aligned16(xstage), "nq_ep_gather: null or misaligned pointer");
+    nq::EpPeers p{};
+    for (int r = 0; r < world; ++r)
+    {
+        NQ_REQUIRE(peer_x[r] && nq::aligned16(peer_x[r]), "nq_ep_gather: buffer of rank %d is null or misaligned", r);
+        p.part[r] = (const float*)peer_x[r];
+    }
+    nq::ep_gather_kernel<<<world * tokens_per_rank, 128, 0, (cudaStream_t)stream>>>((__half*)xstage, p, sel, (const __half*)rw, tokens_per_rank, topk, H,
+                                                                                    rank, experts_per_rank);
+    return nq::check_launch("nq_ep_gather");
+}
 
 extern "C" int nq_ep_combine(float* out, const void* const* peer_parts, const int32_t* rows, int T, int H, int world, void* stream)
 {

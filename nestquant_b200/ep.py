@@ -61,14 +61,21 @@ def _exchange_counts(counts, group):
 
 
 class _PeerRows:
-    """symmetric-memory buffer [rows, H] fp32 per rank for the partial rows of the prefill, with every rank's address"""
+    """symmetric-memory buffers per rank, with every rank's address: partial rows [rows, H] fp32 of the prefill and the
+    rank's own input rows [rows_x, H] fp16"""
 
-    def __init__(s, rows, H, dev, group):
+    def __init__(s, rows, H, dev, group, world):
         import torch.distributed._symmetric_memory as symm
+        g = group if group is not None else dist.group.WORLD
         s.buf = symm.empty(rows, H, dtype=torch.float32, device=dev)
-        s.hdl = symm.rendezvous(s.buf, group if group is not None else dist.group.WORLD)
+        s.hdl = symm.rendezvous(s.buf, g)
         s.rows = rows
         s.ptrs = [int(p) for p in s.hdl.buffer_ptrs]
+        s.rows_x = (rows + world - 1) // world
+        s.xbuf = symm.empty(s.rows_x, H, dtype=torch.float16, device=dev)
+        s.xhdl = symm.rendezvous(s.xbuf, g)
+        s.xptrs = [int(p) for p in s.xhdl.buffer_ptrs]
+        s.xstage = None
 
     def barrier(s):
         s.hdl.barrier()
@@ -88,7 +95,7 @@ class EPLayer:
         if peer_rows > 0 and s.world > 1 and s.world <= 8 and _has_alltoall(group):
             ok = torch.ones(1, dtype=torch.int32, device=local_layer.table.device)
             try:
-                s.peer = _PeerRows(peer_rows, s.H, local_layer.table.device, group)
+                s.peer = _PeerRows(peer_rows, s.H, local_layer.table.device, group, s.world)
             except Exception as e:                      # no peer access / no symmetric memory on this system
                 s.peer_error = repr(e)
                 ok.zero_()
@@ -110,6 +117,8 @@ class EPLayer:
             return s.L.prefill(x, sel, rw)
         T, k = sel.shape
         dev = x.device
+        if s.peer is not None and T * s.world <= s.peer.rows and T <= s.peer.rows_x and s._same_count(T):
+            return s._prefill_peer(x, sel, rw)
         owner = torch.div(sel, s.per, rounding_mode="floor")                       # [T, k] destination rank of each pick
         idx, send_x, send_sel, send_rw = [], [], [], []
         for d in range(s.world):
@@ -157,4 +166,47 @@ class EPLayer:
             if n:
                 out.index_add_(0, idx[d], back[o:o + n])
             o += n
+        return out
+
+    def _same_count(s, T):
+        """every rank brings the same number of tokens (the peer path addresses tokens as rank * T + t)"""
+        c = torch.tensor([T, -T], dtype=torch.int64, device=s.L.table.device)
+        dist.all_reduce(c, op=dist.ReduceOp.MAX, group=s.group)
+        return int(c[0]) == T and int(c[1]) == -T
+
+    def _prefill_peer(s, x, sel, rw):
+        """Exchange over peer memory: only the picks (sel, rw: a few hundred KB) travel by a collective.  Each rank pulls the
+        input rows of the tokens that picked its experts from their owners (nq_ep_gather), runs its local prefill on the
+        global token list with the other ranks' picks zeroed, leaves the partial rows in its symmetric buffer, and every
+        owner sums its tokens' partial rows from the peers in rank order (nq_ep_combine).  No sizes go through the host."""
+        import ctypes as C
+        from .capi import check, lib
+        T, k = sel.shape
+        dev, W, P = x.device, s.world, s.peer
+        st = torch.cuda.current_stream(dev).cuda_stream
+        P.xbuf[:T].copy_(x)
+        sel_all = torch.empty(W * T, k, dtype=sel.dtype, device=dev)
+        rw_all = torch.empty(W * T, k, dtype=rw.dtype, device=dev)
+        dist.all_gather_into_tensor(sel_all, sel.contiguous(), group=s.group)
+        dist.all_gather_into_tensor(rw_all, rw.contiguous(), group=s.group)
+        owner = torch.div(sel_all, s.per, rounding_mode="floor")
+        rw_mine = torch.where(owner == s.rank, rw_all, torch.zeros_like(rw_all))
+        if P.xstage is None or P.xstage.shape[0] < W * T:
+            P.xstage = torch.zeros(W * T, s.H, dtype=torch.float16, device=dev)
+        P.barrier()                                                                # every rank's input rows are in place
+        xp = (C.c_void_p * W)(*P.xptrs)
+        check(lib().nq_ep_gather(P.xstage.data_ptr(), xp, sel_all.data_ptr(), rw_all.data_ptr(), T, k, s.H, W, s.rank, s.per, st), "ep_gather")
+        s.L.prefill(P.xstage[:W * T], sel_all, rw_mine, out=P.buf[:W * T])
+        mine = owner[s.rank * T:(s.rank + 1) * T]                                  # ranks that hold a pick of my tokens
+        live = rw != 0
+        rows = torch.full((W, T), -1, dtype=torch.int32, device=dev)
+        tok = torch.arange(s.rank * T, (s.rank + 1) * T, dtype=torch.int32, device=dev)
+        for d in range(W):
+            rows[d] = torch.where(((mine == d) & live).any(1), tok, rows[d])
+        out = torch.empty(T, s.H, dtype=torch.float32, device=dev)
+        P.barrier()                                                                # every rank's partial rows are complete
+        pp = (C.c_void_p * W)(*P.ptrs)
+        check(lib().nq_ep_combine(out.data_ptr(), pp, rows.data_ptr(), T, s.H, W, st), "ep_combine")
+        P.barrier()                                                                # buffers may be overwritten from here on
+        s.last_stats = dict(dispatch="peer loads", combine="peer loads", dispatch_bytes=None, combine_bytes=None)
         return out

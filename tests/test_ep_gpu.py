@@ -1,6 +1,7 @@
-"""Expert-parallel layer on 2 GPUs (skipped on a single-GPU box): the prefill whose combine reads the partial rows from
-the peers' symmetric-memory buffers (nq_ep_combine) must equal, bit for bit, the all-to-all + indexed-add path, and both
-must match a single-GPU layer holding every expert; decode = replicated tokens + all-reduce."""
+"""Expert-parallel layer on 2 GPUs (skipped on a single-GPU box): the prefill whose exchange runs over peer memory (input
+rows pulled by nq_ep_gather, partial rows summed by nq_ep_combine from the peers' symmetric-memory buffers) must equal, bit
+for bit, the all-to-all + indexed-add path, and both must match a single-GPU layer holding every expert; decode =
+replicated tokens + all-reduce."""
 import os
 
 import pytest
@@ -41,7 +42,7 @@ def _worker(rank, world, port, q):
         y_peer = ep_peer.prefill(xr, selr, rwr)
         y_peer2 = ep_peer.prefill(xr, selr, rwr)
         torch.cuda.synchronize()
-        res = dict(peer_on=ep_peer.peer is not None, combine=ep_peer.last_stats.get("combine"),
+        res = dict(peer_on=ep_peer.peer is not None, combine=ep_peer.last_stats.get("combine"), dispatch=ep_peer.last_stats.get("dispatch"),
                    same=bool(torch.equal(y_a2a, y_peer)) and bool(torch.equal(y_peer, y_peer2)),
                    err=layer_errors(y_peer.cpu().numpy(), ref.cpu().numpy())[1])
         xd, seld, rwd = x[:3].to(dev), sel[:3].to(dev), rw[:3].to(dev)
@@ -66,5 +67,5 @@ def test_prefill_combine_over_peer_memory():
         assert p.exitcode == 0, p.exitcode
     out = dict(q.get(timeout=10) for _ in range(2))
     for rank, r in out.items():
-        assert r["peer_on"] and r["combine"] == "peer loads", (rank, r)
+        assert r["peer_on"] and r["combine"] == "peer loads" and r["dispatch"] == "peer loads", (rank, r)
         assert r["same"] and r["err"] <= 1e-4 and r["decode_err"] <= 1e-4, (rank, r)
