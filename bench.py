@@ -455,7 +455,7 @@ def main():
                 "layer_us": us_total / args.steps, "bytes_per_step": by_total / args.steps,
                 "e2e": {"value": by_total / r1["e2e_us"] / 1e3, "unit": UNIT, "h2d_bytes_per_step": H * 2 + topk * 10,
                         "d2h_bytes_per_step": H * 4, "layer_us": r1["e2e_us"] / args.steps,
-                        "how": "host buffers -> pinned staging -> one CUDA-graph replay (H2D copies, 3 kernels, D2H copy) -> synchronize"},
+                        "how": "host buffers -> pinned staging -> one CUDA-graph replay (one H2D copy of the packed inputs, 3 kernels, D2H copy) -> synchronize"},
                 "gpu_launches": 3 * args.steps,
                 "roofline": {"kernel": "gemv_kernel<0> (gate|up GEMV + SwiGLU)", "bound": "hbm", "achieved": achieved, "peak": peak,
                              "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind + " copy bandwidth",

@@ -329,17 +329,28 @@ class MoELayer:
         is a complete call from host buffers."""
         dev = s.table.device
         g = _Captured()
-        g.x = torch.zeros(B, s.H, dtype=torch.float16, device=dev)
-        g.sel = torch.zeros(B, s.topk, dtype=torch.int64, device=dev)
-        g.rw = torch.zeros(B, s.topk, dtype=torch.float16, device=dev)
+        # the three inputs live in one buffer (sel | x | rw, each 16-byte aligned) so that a call from host memory is a
+        # single host -> device copy
+        up = lambda n: (n + 15) // 16 * 16
+        o_sel, o_x = 0, up(B * s.topk * 8)
+        o_rw = o_x + up(B * s.H * 2)
+        nbytes = o_rw + up(B * s.topk * 2)
+        g.inputs = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        view = lambda buf, o, n, dt, shape: buf[o:o + n].view(dt).view(shape)
+        g.sel = view(g.inputs, o_sel, B * s.topk * 8, torch.int64, (B, s.topk))
+        g.x = view(g.inputs, o_x, B * s.H * 2, torch.float16, (B, s.H))
+        g.rw = view(g.inputs, o_rw, B * s.topk * 2, torch.float16, (B, s.topk))
         g.out = torch.zeros(B, s.H, dtype=torch.float32, device=dev)
         if host_io:
-            g.x_host, g.sel_host, g.rw_host = g.x.cpu().pin_memory(), g.sel.cpu().pin_memory(), g.rw.cpu().pin_memory()
+            g.inputs_host = torch.zeros(nbytes, dtype=torch.uint8).pin_memory()
+            g.sel_host = view(g.inputs_host, o_sel, B * s.topk * 8, torch.int64, (B, s.topk))
+            g.x_host = view(g.inputs_host, o_x, B * s.H * 2, torch.float16, (B, s.H))
+            g.rw_host = view(g.inputs_host, o_rw, B * s.topk * 2, torch.float16, (B, s.topk))
             g.out_host = g.out.cpu().pin_memory()
 
         def body():
             if host_io:
-                g.x.copy_(g.x_host, non_blocking=True); g.sel.copy_(g.sel_host, non_blocking=True); g.rw.copy_(g.rw_host, non_blocking=True)
+                g.inputs.copy_(g.inputs_host, non_blocking=True)
             if with_mailbox is not None:
                 with_mailbox.apply()
             s(g.x, g.sel, g.rw, out=g.out)
