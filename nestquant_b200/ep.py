@@ -117,7 +117,8 @@ class EPLayer:
             return s.L.prefill(x, sel, rw)
         T, k = sel.shape
         dev = x.device
-        if s.peer is not None and T * s.world <= s.peer.rows and T <= s.peer.rows_x and s._same_count(T):
+        # every rank asks the same question in the same order, so all of them take the same path
+        if s.peer is not None and s._same_count(T) and T * s.world <= s.peer.rows and T <= s.peer.rows_x:
             return s._prefill_peer(x, sel, rw)
         owner = torch.div(sel, s.per, rounding_mode="floor")                       # [T, k] destination rank of each pick
         idx, send_x, send_sel, send_rw = [], [], [], []
