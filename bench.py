@@ -349,7 +349,7 @@ def main():
         def layer(i, x):
             out = L(x, sels[i], rws[i])
             if world > 1:
-                dist.all_reduce(out)
+                dist.all_reduce(out)          # 24 KB per token: NCCL's all-reduce beats a barrier + peer-load kernel here
             return out
 
         r = {}

@@ -76,13 +76,20 @@ class _PeerRows:
         s.xhdl = symm.rendezvous(s.xbuf, g)
         s.xptrs = [int(p) for p in s.xhdl.buffer_ptrs]
         s.xstage = None
+        # decode: two alternating [32, H] fp32 buffers for the partial outputs
+        s.dec, s.dec_hdl, s.dec_ptrs, s.dec_turn = [], [], [], 0
+        for _ in range(2):
+            b = symm.empty(32, H, dtype=torch.float32, device=dev)
+            h = symm.rendezvous(b, g)
+            s.dec.append(b); s.dec_hdl.append(h); s.dec_ptrs.append([int(p) for p in h.buffer_ptrs])
+        s.dec_rows = {}
 
     def barrier(s):
         s.hdl.barrier()
 
 
 class EPLayer:
-    def __init__(s, local_layer, rank=None, world=None, group=None, peer_rows=0):
+    def __init__(s, local_layer, rank=None, world=None, group=None, peer_rows=0, peer_decode=False):
         """peer_rows > 0: keep up to that many partial rows per rank in symmetric memory and combine over peer loads
         (NCCL groups on peer-connected GPUs only; silently off where symmetric memory cannot be set up)."""
         s.L, s.group = local_layer, group
@@ -92,6 +99,7 @@ class EPLayer:
         s.per = (s.E + s.world - 1) // s.world
         s.last_stats = {}
         s.peer = None
+        s.peer_decode = peer_decode
         if peer_rows > 0 and s.world > 1 and s.world <= 8 and _has_alltoall(group):
             ok = torch.ones(1, dtype=torch.int32, device=local_layer.table.device)
             try:
@@ -105,9 +113,30 @@ class EPLayer:
 
     # ---- 1..32 replicated tokens
     def decode(s, x, sel, rw, out=None):
-        y = s.L(x, sel, rw) if out is None else s.L(x, sel, rw, out=out)
-        if s.world > 1:
-            dist.all_reduce(y, group=s.group)
+        """1..32 replicated tokens -> the summed [B, H] output on every rank.  With peer buffers: each rank leaves its partial
+        output in a symmetric buffer and, after one barrier, sums all ranks' partials itself by peer loads in rank order
+        (one small kernel, every rank gets bitwise the same result); two buffers alternate so that the barrier of the
+        next call also protects the reads of this one.  Otherwise an all-reduce of the collective library - the default
+        (peer_decode = False): measured on 2 B200s a 1-token call takes 143 us with NCCL's all-reduce and 154 us with the
+        symmetric-memory barrier + combine kernel."""
+        if s.peer is None or not s.peer_decode or s.world == 1 or x.shape[0] > s.peer.dec[0].shape[0]:
+            y = s.L(x, sel, rw) if out is None else s.L(x, sel, rw, out=out)
+            if s.world > 1:
+                dist.all_reduce(y, group=s.group)
+            return y
+        import ctypes as C
+        from .capi import check, lib
+        B, dev = x.shape[0], x.device
+        i = s.peer.dec_turn
+        s.peer.dec_turn ^= 1
+        s.L(x, sel, rw, out=s.peer.dec[i][:B])
+        y = torch.empty(B, s.H, dtype=torch.float32, device=dev) if out is None else out
+        s.peer.dec_hdl[i].barrier()                                                # every rank's partial output is complete
+        pp = (C.c_void_p * s.world)(*s.peer.dec_ptrs[i])
+        if B not in s.peer.dec_rows:                                               # row t of every rank
+            s.peer.dec_rows[B] = torch.arange(B, dtype=torch.int32, device=dev).repeat(s.world, 1).contiguous()
+        check(lib().nq_ep_combine(y.data_ptr(), pp, s.peer.dec_rows[B].data_ptr(), B, s.H, s.world,
+                                  torch.cuda.current_stream(dev).cuda_stream), "ep_combine")
         return y
 
     # ---- sharded tokens

@@ -37,7 +37,7 @@ def _worker(rank, world, port, q):
         xr, selr, rwr = x[sl].to(dev), sel[sl].to(dev), rw[sl].to(dev)
         ref = full.prefill(xr, selr, rwr)
         ep_a2a = EPLayer(part, rank, world)
-        ep_peer = EPLayer(part, rank, world, peer_rows=world * T)
+        ep_peer = EPLayer(part, rank, world, peer_rows=world * T, peer_decode=True)
         y_a2a = ep_a2a.prefill(xr, selr, rwr)
         y_peer = ep_peer.prefill(xr, selr, rwr)
         y_peer2 = ep_peer.prefill(xr, selr, rwr)
@@ -47,7 +47,12 @@ def _worker(rank, world, port, q):
                    err=layer_errors(y_peer.cpu().numpy(), ref.cpu().numpy())[1])
         xd, seld, rwd = x[:3].to(dev), sel[:3].to(dev), rw[:3].to(dev)
         yd = ep_a2a.decode(xd, seld, rwd).clone()
-        res["decode_err"] = layer_errors(yd.cpu().numpy(), full(xd, seld, rwd).cpu().numpy())[1]
+        want = full(xd, seld, rwd).cpu().numpy()
+        res["decode_err"] = layer_errors(yd.cpu().numpy(), want)[1]
+        yp = [ep_peer.decode(xd, seld, rwd).clone() for _ in range(3)]          # alternating buffers, one barrier per call
+        torch.cuda.synchronize()
+        res["decode_peer_err"] = max(layer_errors(y.cpu().numpy(), want)[1] for y in yp)
+        res["decode_peer_same"] = bool(torch.equal(yp[0], yp[1])) and bool(torch.equal(yp[1], yp[2]))
         q.put((rank, res))
     finally:
         dist.destroy_process_group()
@@ -69,3 +74,4 @@ def test_prefill_combine_over_peer_memory():
     for rank, r in out.items():
         assert r["peer_on"] and r["combine"] == "peer loads" and r["dispatch"] == "peer loads", (rank, r)
         assert r["same"] and r["err"] <= 1e-4 and r["decode_err"] <= 1e-4, (rank, r)
+        assert r["decode_peer_err"] <= 1e-4 and r["decode_peer_same"], (rank, r)
