@@ -24,7 +24,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit(__doc__)
+REF = sys.argv[1]
 OUT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(REF, "sm120"))
 sys.modules["build"] = types.SimpleNamespace(get=lambda *a, **k: None, get_sal=lambda *a, **k: None)
