@@ -45,72 +45,52 @@ __device__ __forceinline__ float quad_sum(float d)
     d += __shfl_xor_sync(0xffffffffu, d, 1);
     return d + __shfl_xor_sync(0xffffffffu, d, 2);
 }
-// One CTA per kPrePairs consecutive pairs (pairs are sorted by expert, so they mostly share one expert), one warp per
-// 1024 columns.  The expert's two input scale vectors sit in shared memory (dynamic: 2 H halves) and are reloaded only
-// when the expert changes, so a pair costs one row load and two row stores with no pointer chase in front of them.
-constexpr int kPrePairs = 8;
+// one CTA per pair, one warp per 1024 columns
 __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(const __half* __restrict__ x, const int* __restrict__ pt, const int* __restrict__ pe,
-                                                     const int64_t* __restrict__ table, __half* xg, __half* xu, float* zg, int H, int I, int kperm,
-                                                     int R)
+                                                     const int64_t* __restrict__ table, __half* xg, __half* xu, float* zg, int H, int I, int kperm)
 {
-    extern __shared__ __align__(16) __half su_sm[];          // [su_g | su_u]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5, ng = H / 128;
-    const int p0 = blockIdx.x * kPrePairs, p1 = p0 + kPrePairs < R ? p0 + kPrePairs : R;
-    int cur = -1;
-    for (int p = p0; p < p1; ++p)
+    const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int64_t* row = table + (int64_t)pe[p] * kTableWidth;
+    const int level = (int)row[0];
+    if (level <= 0) return;
+    const __half* scales = (const __half*)row[9];
+    const __half* su_u = scales + 2 * H + 3 * I;
+    const __half* xr = x + (size_t)pt[p] * H;
+    const int ng = H / 128;
+    for (int g0 = warp * 8; g0 < ng; g0 += nwarp * 8)
     {
-        const int e = pe[p];
-        const int64_t* row = table + (int64_t)e * kTableWidth;
-        const int level = (int)row[0];
-        if (level <= 0) continue;                             // CTA-uniform
-        if (e != cur)
-        {
-            const __half* scales = (const __half*)row[9];
-            __syncthreads();                                  // everyone is done with the previous expert's vectors
-            for (int i = threadIdx.x; i < H / 8; i += blockDim.x)
-            {
-                ((uint4*)su_sm)[i] = ((const uint4*)scales)[i];
-                ((uint4*)(su_sm + H))[i] = ((const uint4*)(scales + 2 * H + 3 * I))[i];
-            }
-            __syncthreads();
-            cur = e;
-        }
-        const __half* xr = x + (size_t)pt[p] * H;
-        for (int g0 = warp * 8; g0 < ng; g0 += nwarp * 8)
-        {
-            const int grp = g0 + (lane >> 2), k = grp * 128, q = lane & 3;
-            const bool live = grp < ng;
-            uint32_t xw[16];
-            float v[32];
-            if (live) load16w_mapH(xr + k, q, xw);
+        const int grp = g0 + (lane >> 2), k = grp * 128, q = lane & 3;
+        const bool live = grp < ng;
+        uint32_t xw[16];
+        float v[32];
+        if (live) load16w_mapH(xr + k, q, xw);
 #pragma unroll
-            for (int up = 0; up < 2; ++up)
-            {
-                if (live) mul32h_mapH(xw, su_sm + up * H + k, q, v);
-                else
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = 0.f;
-                wht128_x8(v, lane);
-                if (kperm) store32h_mapH_kperm((up ? xu : xg) + (size_t)p * H + k, q, v, live);
-                else if (live) store32h_mapH((up ? xu : xg) + (size_t)p * H + k, q, v);
-            }
-        }
-        const LowRank L = low_rank_of(row, level);
-        for (int r = warp; r < 4; r += nwarp)
+        for (int up = 0; up < 2; ++up)
         {
-            float d = 0.f;
-            if (r < L.rg)
-            {
-                for (int k = lane * 4; k < H; k += 128)
-                {
-                    float f[4], v[4];
-                    load4h(xr + k, f); load4h(L.lr + (size_t)r * H + k, v);
-                    d += f[0] * v[0] + f[1] * v[1] + f[2] * v[2] + f[3] * v[3];
-                }
-                d = warp_sum(d);
-            }
-            if (lane == 0) zg[(size_t)p * 4 + r] = d;
+            if (live) mul32h_mapH(xw, (up ? su_u : scales) + k, q, v);
+            else
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            wht128_x8(v, lane);
+            if (kperm) store32h_mapH_kperm((up ? xu : xg) + (size_t)p * H + k, q, v, live);
+            else if (live) store32h_mapH((up ? xu : xg) + (size_t)p * H + k, q, v);
         }
+    }
+    const LowRank L = low_rank_of(row, level);
+    for (int r = warp; r < 4; r += nwarp)
+    {
+        float d = 0.f;
+        if (r < L.rg)
+        {
+            for (int k = lane * 4; k < H; k += 128)
+            {
+                float f[4], v[4];
+                load4h(xr + k, f); load4h(L.lr + (size_t)r * H + k, v);
+                d += f[0] * v[0] + f[1] * v[1] + f[2] * v[2] + f[3] * v[3];
+            }
+            d = warp_sum(d);
+        }
+        if (lane == 0) zg[(size_t)p * 4 + r] = d;
     }
 }
 
@@ -310,8 +290,7 @@ int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const 
     NQ_REQUIRE(x && pt && pe && table && xg && xu && zg, "nq_pf_pre: null pointer");
     NQ_SHAPE_OK("nq_pf_pre");
     NQ_REQUIRE(nq::aligned16(x) && nq::aligned16(xg) && nq::aligned16(xu), "nq_pf_pre: x, xg, xu must be 16-byte aligned");
-    nq::pf_pre_kernel<<<(R + nq::kPrePairs - 1) / nq::kPrePairs, nq::pf_threads(H), (size_t)H * 4, (cudaStream_t)stream>>>(
-        (const __half*)x, pt, pe, table, (__half*)xg, (__half*)xu, zg, H, I, kperm, R);
+    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>((const __half*)x, pt, pe, table, (__half*)xg, (__half*)xu, zg, H, I, kperm);
     return nq::check_launch("nq_pf_pre");
 }
 
