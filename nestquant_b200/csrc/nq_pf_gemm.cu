@@ -37,19 +37,25 @@ namespace nq {
 #ifndef NQ_PF_SPLIT
 #define NQ_PF_SPLIT 256      // token tiles wider than this are multiplied as two column halves
 #endif
-constexpr int kPfTokens = 384;                       // tokens per pass = accumulator columns
-constexpr int kPfTmemCols = 512;                     // [0, 384) accumulator, [384, 512) weight tiles
-constexpr int kPfAccCols = 384;
-constexpr int kPfAStages = 4;                        // weight tiles in tensor memory: each unit fills two consecutive stages
+#ifndef NQ_PF_GROUPS
+#define NQ_PF_GROUPS 2      // groups of 8 decode warps; group g takes the chunks c = g (mod groups) of its strips.  3 groups
+                            // (24 decode warps at 72 registers) measured the same time as 2: the kernel runs at the power cap
+#endif
+constexpr int kPfGroups = NQ_PF_GROUPS;
+constexpr int kPfDecodeWarps = 8 * kPfGroups;
+constexpr int kPfAStages = 2 * kPfGroups;            // weight tiles in tensor memory: each unit fills two consecutive stages
 constexpr int kPfACols = 32;                         // [128 lanes x 64 k] fp16 = 32 columns
+constexpr int kPfTmemCols = 512;                     // [0, kPfAccCols) accumulator, the rest weight tiles
+constexpr int kPfAccCols = kPfTmemCols - kPfAStages * kPfACols;
+constexpr int kPfTokens = kPfAccCols;                // tokens per pass = accumulator columns (384 with 2 groups, 320 with 3)
 constexpr int kPfBoxRows = 64;                       // token rows per TMA box
 constexpr int kPfBoxBytes = kPfBoxRows * 128;        // [64 rows][64 k] fp16
 constexpr int kPfBBoxes = 20;                        // token-tile region: 8 x 2, 5 x 4, 4 x 5 or 3 x 6 boxes per stage
 constexpr int kPfBStages = 8;                        // most token-tile stages
 constexpr int kPfRingDepth = 2;
-constexpr int kPfDecodeWarps = 16;
 constexpr int kPfThreads = 32 * (2 + kPfDecodeWarps);
 constexpr int kPfSmem = kPfBBoxes * kPfBoxBytes + kPfDecodeWarps * kPfRingDepth * kStageBytes + 1024 + 256;
+static_assert(kPfSmem <= 232448, "shared memory of the prefill GEMM");
 constexpr unsigned long long kPfWaitNs = 2000000000ull;   // a wait that lasts 2 s is treated as a hang
 
 struct PfPass { int expert, row0, ntok, pad; };
@@ -284,11 +290,11 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
     auto res_unit = [&](int ch) -> size_t {
         return P.flags ? (size_t)strip * nm + __popcll(fl & ((1ull << ch) - 1ull)) : unit0 + ch;
     };
-    // per-unit scalars of this warp's chunks, one chunk (group + 2 * lane) per lane: ring signs and, for refined units,
+    // per-unit scalars of this warp's chunks, one chunk (group + kPfGroups * lane) per lane: ring signs and, for refined units,
     // the block word with its fp16 multiplier / addend (computed once here instead of by every lane of every unit)
     uint32_t var_b = 0, ac = 0, mbn = 0;
     {
-        const int ch = group + 2 * lane;
+        const int ch = group + kPfGroups * lane;
         if (ch < C)
         {
             if (P.var) var_b = __ldg(P.var + unit0 + ch);
@@ -309,14 +315,14 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
 #pragma unroll
     for (int d = 0; d < kPfRingDepth - 1; ++d)
     {
-        if (group + 2 * d < C) issue(group + 2 * d, ring + d * kStageBytes);
+        if (group + kPfGroups * d < C) issue(group + kPfGroups * d, ring + d * kStageBytes);
         cp_async_commit();
     }
     int slot = 0, slot_in = kPfRingDepth - 1, i = 0;
     bool ok = true;
-    for (int ch = group; ch < C; ch += 2, ++i)
+    for (int ch = group; ch < C; ch += kPfGroups, ++i)
     {
-        if (ch + 2 * (kPfRingDepth - 1) < C) issue(ch + 2 * (kPfRingDepth - 1), ring + slot_in * kStageBytes);
+        if (ch + kPfGroups * (kPfRingDepth - 1) < C) issue(ch + kPfGroups * (kPfRingDepth - 1), ring + slot_in * kStageBytes);
         cp_async_commit();
         cp_async_wait<kPfRingDepth - 1>();
         const uint8_t* st = ring + slot * kStageBytes;
@@ -403,7 +409,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
     if (threadIdx.x == 0)
     {
         for (int s = 0; s < kPfBStages; ++s) { mbar_init(&sh->full_b[s], 1); mbar_init(&sh->empty_b[s], 1); }
-        for (int s = 0; s < kPfAStages; ++s) { mbar_init(&sh->full_a[s], kPfDecodeWarps / 2); mbar_init(&sh->empty_a[s], 1); }
+        for (int s = 0; s < kPfAStages; ++s) { mbar_init(&sh->full_a[s], 8); mbar_init(&sh->empty_a[s], 1); }
         mbar_init(&sh->acc_full, 1); mbar_init(&sh->acc_empty, kPfDecodeWarps);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -440,7 +446,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
         const int ncol = (up ? wg - a.I / 128 : wg) * 128 + q * 32 + lane;
         float* out = up ? a.out1 : a.out0;
         const int ld = a.down ? a.H : a.I;
-        for (int c0 = cpart * 32; c0 < ps.ntok; c0 += 128)
+        for (int c0 = cpart * 32; c0 < ps.ntok; c0 += 32 * (kPfDecodeWarps / 4))
         {
             uint32_t v[32];
             tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c0, v);
@@ -516,15 +522,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
         {
             // ---- decode, then epilogue
             // A warp may touch only the 32 tensor-memory lanes of its quarter (warp % 4): the four decode warps of a
-            // quarter take its two strips x the two chunk parities.
-            const int dw = warp - 2, qd = warp & 3, sub = (dw >> 2) & 1, half = dw >> 3, sidx = 2 * qd + sub;
+            // quarter take its two strips x the chunk groups.
+            const int dw = warp - 2, qd = warp & 3, sub = (dw >> 2) & 1, half = dw >> 3, sidx = 2 * qd + sub;      // half = chunk group
             const uint32_t tmem_a = tmem + ((uint32_t)(32 * qd + 16 * sub) << 16) + kPfAccCols;
             const int64_t* row = a.table + (int64_t)ps.expert * kTableWidth;
             const int level = (int)row[0];
             const ProjPlanes P = planes_from_row(row, a.down);
             const int rc = (int)row[10 + a.down], nm = a.down ? a.nm_dn : a.nm_gu, bk = (int)(row[19] >> (8 * a.down)) & 0xFF;
             uint8_t* ring = rings + dw * kPfRingDepth * kStageBytes;
-            // group `half` of 8 warps decodes the chunks of that parity: k-blocks 4 i + 2 half and + 1.  The epilogue
+            // group `half` of 8 warps decodes the chunks c = half (mod kPfGroups): k-blocks 2 c and 2 c + 1.  The epilogue
             // of the previous item runs after this item's first unit is decoded: the MMAs of the previous item's last
             // k-blocks finish meanwhile, and the tensor pipe finds tiles waiting when the accumulator is free again.
             auto mid = [&]() { if (have_prev) { epilogue(prev, prev_wg, prev_up, nitem - 1); have_prev = false; } };
