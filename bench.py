@@ -413,7 +413,9 @@ def main():
     T_pf = 8192
     own = set(owned)
     Lp, _ = synth.build_layer(cfg, [4 if e in own else 0 for e in range(E)], seed=SEED + 1, dev=dev, Bmax=1, owned=owned)
-    ep = EPLayer(Lp, rank, world, peer_rows=T_pf) if world > 1 else None     # partial rows combined over peer loads
+    # exchange over peer memory where it has been run on hardware (2 ranks; NQ_EP_PEER=1 forces it for more), NCCL all-to-all otherwise
+    use_peer = world == 2 or os.environ.get("NQ_EP_PEER") == "1"
+    ep = EPLayer(Lp, rank, world, peer_rows=T_pf if use_peer else 0) if world > 1 else None
     Tl = T_pf // world
     selp, rwp = synth.routing(T_pf, E, topk, SEED + 99)
     xp = synth.tokens(T_pf, H, SEED + 98)
