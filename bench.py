@@ -135,6 +135,11 @@ def oracle_step(experts_np, levels, x, sel, rw, picks=None):
 
 def run_reference(args):
     """CPU arm: the oracle port of the reference's torch path, all host threads, on a bounded sample per step."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # the launcher pins every rank to one OpenMP thread; this arm runs on rank 0 alone and may use the whole host
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     import numpy as np
     import torch
     from nestquant_b200 import moe, synth
