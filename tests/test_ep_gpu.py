@@ -75,3 +75,35 @@ def test_prefill_combine_over_peer_memory():
         assert r["peer_on"] and r["combine"] == "peer loads" and r["dispatch"] == "peer loads", (rank, r)
         assert r["same"] and r["err"] <= 1e-4 and r["decode_err"] <= 1e-4, (rank, r)
         assert r["decode_peer_err"] <= 1e-4 and r["decode_peer_same"], (rank, r)
+
+
+def test_exchange_kernels_on_one_gpu():
+    """nq_ep_gather / nq_ep_combine with the buffers of three emulated ranks on one device (the kernels only see addresses):
+    the gathered rows and the rank-ordered sums must equal plain indexing."""
+    import ctypes as C
+    from nestquant_b200.capi import check, lib
+    W, T, k, H, per, rank = 3, 50, 4, 256, 4, 1
+    g = torch.Generator().manual_seed(21)
+    xs = [torch.randn(T, H, generator=g).half().cuda() for _ in range(W)]
+    sel = torch.randint(0, W * per, (W * T, k), generator=g).cuda()
+    rw = torch.rand(W * T, k, generator=g).half().cuda()
+    rw[5] = 0                                              # a token without any weight is not fetched
+    stage = torch.full((W * T, H), 7.0, dtype=torch.float16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    ptrs = (C.c_void_p * W)(*[x.data_ptr() for x in xs])
+    check(lib().nq_ep_gather(stage.data_ptr(), ptrs, sel.data_ptr(), rw.data_ptr(), T, k, H, W, rank, per, st), "ep_gather")
+    need = (((sel // per) == rank) & (rw != 0)).any(1)
+    want = torch.where(need[:, None], torch.cat(xs), torch.full_like(stage, 7.0))
+    torch.cuda.synchronize()
+    assert torch.equal(stage, want) and 0 < int(need.sum()) < W * T and not bool(need[5])
+    parts = [torch.randn(W * T, H, generator=g).cuda() for _ in range(W)]
+    rows = torch.randint(-1, W * T, (W, T), generator=g, dtype=torch.int32).cuda()
+    out = torch.empty(T, H, device="cuda")
+    pp = (C.c_void_p * W)(*[p.data_ptr() for p in parts])
+    check(lib().nq_ep_combine(out.data_ptr(), pp, rows.data_ptr(), T, H, W, st), "ep_combine")
+    ref = torch.zeros(T, H, device="cuda")
+    for r in range(W):                                     # rank order
+        ok = rows[r] >= 0
+        ref = ref + torch.where(ok[:, None], parts[r][rows[r].clamp(min=0).long()], torch.zeros_like(ref))
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref)
