@@ -14,7 +14,7 @@
  *   [0] level (0 = not resident here, 2, 4)   [1..4] gate|up: base, p4, d4, flags (0 = dense)   [5..8] down: same
  *   [9] fp16 scales [H su_g | I sv_g | I sv_u | I su_d | H sv_o | H su_u]   [10],[11] residual window codes
  *   [12],[13] ring-sign planes (0 = none)   [14] low-rank plane, [15] its level-4 part, [16] r_gu, [17] r_dn
- *   [18] width of the down-input rotation (0 or 128, or 512)   [19] base window codes (must be 0)
+ *   [18] width of the down-input rotation (0 or 128, or 512)   [19] base window codes bk_gu | bk_dn << 8 (0, or 1: see nq_bk_codes)
  */
 #ifndef NESTQUANT_B200_H
 #define NESTQUANT_B200_H
@@ -80,28 +80,31 @@ int nq_promote(void* slot, const void* host_record, size_t record_bytes, int64_t
  * R = number of pairs in this call.  z arrays are fp32 [R][4] (low-rank inputs, rank <= 4). */
 
 /* xg[p] = fp16(WHT128(x[pt[p]] * su_g)), xu[p] likewise with su_u, both [R][H]; zg[p][r] = x . V_gu[r].
- * Pairs of level-0 experts are skipped (their rows are left untouched).
+ * Pairs of level-0 experts and pairs whose expert id is outside [0, E) (padding) are skipped (their rows are left untouched).
  * kperm != 0 writes xg / xu in the k order nq_pf_gemm reads: inside every 16 consecutive k, position 4 i + {0, 1}
  * holds k = 2 i + {0, 1} and position 4 i + {2, 3} holds k = 8 + 2 i + {0, 1} (i < 4); 0 = plain order (the reference's).
  * Replaces pf_pre() (sm120/nqmoe.cu:1081-1117,1258-1267). */
-int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const int64_t* table, void* xg, void* xu, float* zg,
+int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const int64_t* table, int E, void* xg, void* xu, float* zg,
               int H, int I, int kperm, void* stream);
 
 /* acc_g, acc_u fp32 [R][I] (GEMM outputs) -> h fp16 [R][I] = WHT_w(silu(g) u su_d), g = WHT128(acc_g) sv_g + low rank,
  * w = 128 or the expert's 512-wide rotation; zd[p][r] = (silu(g) u) . V_dn[r].  kperm: k order of h as for nq_pf_pre.
  * Replaces pf_mid() (sm120/nqmoe.cu:1118-1203,1268-1277). */
-int nq_pf_mid(const float* acc_g, const float* acc_u, const float* zg, const int32_t* pe, int R, const int64_t* table, void* h,
+int nq_pf_mid(const float* acc_g, const float* acc_u, const float* zg, const int32_t* pe, int R, const int64_t* table, int E, void* h,
               float* zd, int H, int I, int kperm, void* stream);
 
 /* out[pt[p]] += prw[p] * (WHT128(y[p]) * sv_o + low rank), y fp32 [R][H]; atomic adds into a caller-zeroed out.
  * Replaces pf_post() (sm120/nqmoe.cu:1204-1240,1278-1287). */
-int nq_pf_post(const float* y, const float* zd, const int32_t* pt, const int32_t* pe, const void* prw, int R, const int64_t* table,
+int nq_pf_post(const float* y, const float* zd, const int32_t* pt, const int32_t* pe, const void* prw, int R, const int64_t* table, int E,
                float* out, int H, int I, void* stream);
 
-/* Same sum without atomics: out[t] = sum over k in pick order of the pair at pos[t * topk + k]; out [T][H] is
- * overwritten and bitwise repeatable.  No counterpart in the reference (its pf_post order depends on atomics). */
+/* Same sum without atomics, one window of the expert-sorted pair list at a time: y / zd hold the rows of the pairs
+ * [pair0, pair0 + npairs) (row = pair index - pair0); pos[t * topk + k] = pair index of that pick.  Each token's picks
+ * inside the window are added in pick order.  accumulate = 0: out[t] is overwritten (zeros for a token without a pick in
+ * the window); accumulate = 1: the sum is added to out[t].  Window after window in a fixed order this is bitwise
+ * repeatable with scratch for one window only.  No counterpart in the reference (its pf_post order depends on atomics). */
 int nq_pf_combine(const float* y, const float* zd, const int32_t* pos, const int64_t* sel, const void* rw, int T, int topk,
-                  const int64_t* table, int E, float* out, int H, int I, void* stream);
+                  const int64_t* table, int E, float* out, int H, int I, int pair0, int npairs, int accumulate, void* stream);
 
 /* Fused prefill GEMM (decode in registers -> weight tiles in tensor memory -> tcgen05.mma): the replacement of the reference's
  * pf_decode + grouped GEMM pair (sm120/moe.py:303-324, sm120/pf_gemm.py:7-34, sm120/nqmoe.cu:1013-1080); the dense fp16
@@ -130,12 +133,22 @@ int nq_pf_hits(const int32_t* counts, int32_t* hits, int E, void* stream);
  *   - split-k partial sums are written to acc_gu / acc_d and summed in a fixed order: results are bitwise repeatable,
  *     and those two buffers need no zeroing.  cnt_gu, cnt_d and wq must be zero on entry and are zero again on exit;
  *   - workspace sizes depend on the k-splits: ask nq_moe_workspace() (the reference sized them from B * topk alone);
- *     h also holds the rotated inputs and cnt_h holds the run list;
+ *     h also holds the rotated inputs;
+ *   - cnt_h[0] is a status word: the call leaves it alone unless a device-side wait ran out (2 s), then it is 1 and the
+ *     outputs are invalid.  Clear it before the first call and read it after synchronising if you want to know;
  *   - if no resident expert with a non-zero weight is picked at all, out is written with zeros
- *     (the reference leaves it untouched, sm120/nqmoe.cu:789);
+ *     (the reference leaves it untouched, sm120/nqmoe.cu:789); so is the row of any token none of whose picks is resident;
  *   - tiling is two integers (ks_gu, ks_dn = k-slices per strip) instead of cfg_gu / cfg_dn = (cpw, sb, nst[, pers]).
- * Three launches on `stream`; every routing, level and pointer decision is read on the device, so the call can be
- * captured in a CUDA graph and replayed while a mailbox flips table rows. */
+ * One persistent launch on `stream` does the routing, the input rotations, both GEMVs and the combine (the reference: two
+ * launches); every routing, level and pointer decision is read on the device, so the call can be captured in a CUDA graph
+ * and replayed while a mailbox flips table rows.
+ * which = 1 stops after h (gate|up, SwiGLU); which = 2 starts from the h that is in the workspace.  Both h [S][I] and the
+ * rotated inputs [S][2][H] behind it are fp16 in "operand order": inside every 128 consecutive k, element
+ * k = 16 T + 2 t4 + 8 hi + e (T < 8, t4 < 4, hi, e < 2) sits at position 32 t4 + 4 T + 2 hi + e.  With which = 1 the
+ * split-k partial sums of the gate|up projection stay readable in acc_gu [ks_gu][S][2I], with which = 2 those of the down
+ * projection in acc_d [ks_dn][S][H] (S = B * topk pick slots): fed one-hot inputs they hold columns of the decoded weight
+ * matrices, which is how the tests check the decoder inside this kernel bit for bit (the role of the reference's
+ * NQ_WDUMP hook, sm120/nqmoe.cu:246-248,852-853). */
 typedef struct NqMoeWorkspace {
     size_t acc_gu_floats, h_halves, acc_d_floats, cnt_gu_ints, cnt_d_ints, wq_ints, zd_floats, cnt_h_ints;
 } NqMoeWorkspace;

@@ -55,10 +55,10 @@ SIGNATURES = {
     "nq_pf_decode": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
     "nq_mailbox": (_i, [_p, _p, _p, _p, _p, _i, _p]),
     "nq_promote": (_i, [_p, _p, _sz, _p, _p, _p, _p, _p]),
-    "nq_pf_pre": (_i, [_p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _p]),
-    "nq_pf_mid": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _p]),
-    "nq_pf_post": (_i, [_p, _p, _p, _p, _p, _i, _p, _p, _i, _i, _p]),
-    "nq_pf_combine": (_i, [_p, _p, _p, _p, _p, _i, _i, _p, _i, _p, _i, _i, _p]),
+    "nq_pf_pre": (_i, [_p, _p, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _p]),
+    "nq_pf_mid": (_i, [_p, _p, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _p]),
+    "nq_pf_post": (_i, [_p, _p, _p, _p, _p, _i, _p, _i, _p, _i, _i, _p]),
+    "nq_pf_combine": (_i, [_p, _p, _p, _p, _p, _i, _i, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
     "nq_pf_hits": (_i, [_p, _p, _i, _p]),
     "nq_pf_plan_ints": (_i, [_i, _i]),
     "nq_pf_plan": (_i, [_p, _p, _i, _i, _p, _i, _p]),

@@ -3,12 +3,25 @@
 // Format (reference: sm120/ref15_spec.py:3-8,43-90; sm120/nqmoe.cu:14-25,146-173; sm120/moe.py:36-63):
 //   unit    = 16 rows x 128 k = 32 lane records; record index ((strip * C + chunk) * 32 + lane); lane = 4 g + t4.
 //   ring g  = records of lanes 4g..4g+3 concatenated LSB-first (tail-biting); lane weight j is ring position 64 t4 + j.
-//   state   = 16-bit window at bit step_off(j) of the lane stream, continued into the next ring lane's first word.
+//   state   = 16-bit window at bit step_offset(j) of the lane stream, continued into the next ring lane's first word.
 //   S       = sum of the four bytes of state * 0x83DCD12D.
 //   level 2 : Q = fp16(A (1024 + Sb) + B), A = 0x1eee, B = 0xc931.
 //   level 4 : F = (Mb Sb + N Sr + 128) >> 8, Q = fp16(A' (1024 + F) + C'), A'/C' from the unit's block word.
 //   lane weight j = 2 pp + e, pp = 4 t + r  ->  row g + 8 (r & 1), k = 16 t + 2 t4 + 8 (r >> 1) + e, i.e. pair pp is
 //   register r of the m16n8k16 A fragment of k-step t.
+//
+// How a k-step (8 weights of a lane) is decoded here:
+//   windows   the 64 window offsets of a code are known at compile time.  Windows whose offsets agree modulo 8 are
+//             packed greedily, in stream order, into 32-bit "views" of the stream (one funnel shift each, none when the
+//             view starts on a word); a view serves up to three windows, at its byte offsets 0, 1 and 2, each by one
+//             instruction (and / byte-permute / shift).
+//   hash      one 32-bit multiply per window.
+//   byte sums SUM_MMA: one mma.m16n8k32.u8 adds the bytes of four hashed words per lane at once: the hashed words are
+//             the A fragment, the B fragment is a per-lane selector (each lane's own k-group routed to its own two
+//             accumulator columns) whose non-zero bytes are 1 (level 2) or Mb, N (level 4, second MMA chained through the
+//             accumulator), and the accumulator starts at the bit pattern that turns the sum into fp16(1024 + S).
+//             SUM_DP4A: the same sums by one dp4a per hashed word (two at level 4).
+//   affine    one byte-permute packs two sums, one fp16x2 fma applies the unit's multiplier and addend (single rounding).
 #pragma once
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -22,7 +35,13 @@ constexpr uint32_t kMul1B2 = 0xc931c931u;   // fp16x2 B
 constexpr int kTableWidth = 20;              // int64 words per expert row of the device table
 constexpr int kNumCodes = 10;
 
-// ---------------------------------------------------------------- window patterns
+enum { SUM_DP4A = 0, SUM_MMA = 1 };
+#ifndef NQ_SUM
+#define NQ_SUM 1
+#endif
+constexpr int kSumDefault = NQ_SUM;
+
+// ---------------------------------------------------------------- window patterns (the format's tables)
 __host__ __device__ constexpr int pattern_ka(int code)
 {
     constexpr int t[kNumCodes] = {2, 1, 2, 2, 3, 1, 1, 2, 1, 2};
@@ -47,13 +66,13 @@ __host__ __device__ constexpr int step_offset(int j, int code)
     for (int i = 0; i < (j & 15); ++i) s += ka + ((mask >> i) & 1);
     return s;
 }
+__host__ __device__ constexpr int record_bits(int code) { return 4 * (16 * pattern_ka(code) + popcount16(pattern_mask(code))); }
 template <int CODE>
 struct Pattern
 {
-    static constexpr int kBits = 4 * (16 * pattern_ka(CODE) + popcount16(pattern_mask(CODE)));   // bits per lane record
+    static constexpr int kBits = record_bits(CODE);     // bits per lane record
     static constexpr int kWords = (kBits + 31) / 32;
 };
-__host__ __device__ constexpr int record_bits(int code) { return 4 * (16 * pattern_ka(code) + popcount16(pattern_mask(code))); }
 
 template <int... Is, class F>
 __device__ __forceinline__ void static_for_impl(std::integer_sequence<int, Is...>, F&& f)
@@ -64,44 +83,51 @@ template <int N, class F>
 __device__ __forceinline__ void static_for(F&& f) { static_for_impl(std::make_integer_sequence<int, N>{}, static_cast<F&&>(f)); }
 
 // ---------------------------------------------------------------- 16-bit windows of a lane stream held in registers
-// w[] holds the record words followed by two continuation words (see extend_stream).  Windows that start on a
-// byte boundary inside one word cost one instruction; the others share a 32-bit funnel anchored every 24 bits
-// within their (offset mod 8) class, so one funnel shift serves up to three windows.
-template <int O>
-__device__ __forceinline__ uint32_t window16(const uint32_t* w)
+// View of window j: the offset of the first window, in stream order, of j's residue class (offset mod 8) that lies
+// within 16 bits before j and is not itself covered by an earlier view.
+__host__ __device__ constexpr int view_start(int j, int code)
 {
-    constexpr int i = O >> 5, s = O & 31;
-    if constexpr (s == 0) return w[i] & 0xFFFFu;
-    else if constexpr (s == 8) return __byte_perm(w[i], 0u, 0x4421);
-    else if constexpr (s == 16) return w[i] >> 16;
-    else
+    const int oj = step_offset(j, code);
+    int v = -1;
+    for (int i = 0; i <= j; ++i)
     {
-        constexpr int r = O & 7, a = r + 24 * ((O - r) / 24), ai = a >> 5, as = a & 31, b = (O - a) >> 3;
-        uint32_t f;
-        if constexpr (as == 0) f = w[ai];
-        else f = __funnelshift_r(w[ai], w[ai + 1], as);
-        if constexpr (b == 0) return f & 0xFFFFu;
-        else if constexpr (b == 1) return __byte_perm(f, 0u, 0x4421);
-        else return f >> 16;
+        const int oi = step_offset(i, code);
+        if (((oi ^ oj) & 7) != 0) continue;
+        if (v < 0 || oi > v + 16) v = oi;
     }
+    return v;
+}
+// w[] = the record's words followed by the continuation word(s) (see continue_stream)
+template <int CODE, int J>
+__device__ __forceinline__ uint32_t state16(const uint32_t* w)
+{
+    constexpr int o = step_offset(J, CODE), v = view_start(J, CODE), vi = v >> 5, vs = v & 31, byte = (o - v) >> 3;
+    static_assert(byte >= 0 && byte <= 2 && ((o - v) & 7) == 0, "window outside its view");
+    uint32_t view;
+    if constexpr (vs == 0) view = w[vi];
+    else view = __funnelshift_r(w[vi], w[vi + 1], vs);      // identical views of different windows are merged by the compiler
+    if constexpr (byte == 0) return view & 0xFFFFu;
+    else if constexpr (byte == 1) return __byte_perm(view, 0u, 0x4421);
+    else return view >> 16;
 }
 
-// stream bits [BITS, BITS + 32) = first word of the next lane of the ring
+// A lane's stream continues with the first word of the next lane of its ring (lanes 4g..4g+3, cyclic): append that
+// word at bit BITS.  The array must hold kWords + 2 words.
 template <int BITS>
-__device__ __forceinline__ void extend_stream(uint32_t* w, uint32_t next_first)
+__device__ __forceinline__ void continue_stream(uint32_t* w, uint32_t next_word)
 {
-    constexpr int NW = (BITS + 31) / 32, T = BITS % 32;
-    if constexpr (T == 0) { w[NW] = next_first; w[NW + 1] = 0u; }
+    constexpr int n = (BITS + 31) / 32, used = BITS & 31;
+    if constexpr (used == 0) w[n] = next_word;
     else
     {
-        w[NW - 1] = (w[NW - 1] & ((1u << T) - 1u)) | (next_first << T);
-        w[NW] = next_first >> (32 - T);
-        w[NW + 1] = 0u;
+        w[n - 1] = __funnelshift_l(w[n - 1] << (32 - used), next_word, used);   // low `used` bits kept, the rest from next_word
+        w[n] = next_word >> (32 - used);
     }
+    w[n + 1] = 0u;
 }
-// lane that holds the next quarter of this lane's ring
-__device__ __forceinline__ int ring_next_lane(int lane) { return (lane & ~3) | ((lane + 1) & 3); }
+__device__ __forceinline__ int ring_successor(int lane) { return (lane & 28) | ((lane + 1) & 3); }
 
+// ---------------------------------------------------------------- byte sums and the affine map
 __device__ __forceinline__ uint32_t dot4(uint32_t a, uint32_t b, uint32_t c)
 {
     uint32_t d;
@@ -114,60 +140,135 @@ __device__ __forceinline__ uint32_t fma_h2(uint32_t a, uint32_t b, uint32_t c)
     asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
+// d[i] = c[i] + sum over the lane's own hashed bytes selected by (b0, b1): see ByteSelect
+__device__ __forceinline__ void mma_bytes(uint32_t (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
+                                          uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3)
+{
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+}
+// Selector fragment of the byte-sum MMA.  In m16n8k32 lane (g, t4) owns A columns k = 4 t4 .. 4 t4 + 3 (registers 0, 1:
+// rows g, g + 8) and k = 16 + 4 t4 .. (registers 2, 3), and accumulator columns 2 t4, 2 t4 + 1.  B[k][n] is non-zero
+// only for (k in 4 t4 .. 4 t4 + 3, n = 2 t4) and (k in 16 + 4 t4 .., n = 2 t4 + 1), so d0, d1 = byte sums of A registers
+// 0, 2 (row g) and d2, d3 = of registers 1, 3 (row g + 8): every lane gets the sums of its own four words back.
+// The B fragment of lane (g, t4) holds column n = g: its first register (k = 4 t4 ..) is live iff g == 2 t4, its
+// second (k = 16 + 4 t4 ..) iff g == 2 t4 + 1.
+struct ByteSelect
+{
+    uint32_t even, odd;     // all-ones byte masks
+};
+__device__ __forceinline__ ByteSelect byte_select(int lane)
+{
+    const int g = lane >> 2, t4 = lane & 3;
+    ByteSelect s;
+    s.even = g == 2 * t4 ? 0xFFFFFFFFu : 0u;
+    s.odd = g == 2 * t4 + 1 ? 0xFFFFFFFFu : 0u;
+    return s;
+}
 
-// per-unit multipliers.  level 2: a2 = A, c2 = B.  level 4: from the block word, computed with individually
-// rounded fp32 operations in the order the format defines (sm120/ref15_spec.py:79-83, sm120/moe.py:130-132).
+// Per-unit multipliers.  a2 / c2: fp16x2 multiplier and addend with the ring sign folded in (negating both negates the
+// result exactly).  level 2: weights of both byte sums are 1.  level 4: Mb for the base sum, N for the residual sum.
+// SUM_MMA keeps them as selector fragments (m0, m1 / n0, n1), SUM_DP4A as replicated bytes in m0 / n0.
 struct UnitConsts
 {
-    uint32_t a2, c2;       // fp16x2 multiplier / addend (ring sign folded in)
-    uint32_t mrep, nrep;   // Mb, N replicated into 4 bytes
+    uint32_t a2, c2;
+    uint32_t m0, m1, n0, n1;
 };
-__device__ __forceinline__ UnitConsts consts_level2(uint32_t sign2)
+// Block word Mb | N << 8 -> fp16 multiplier A' (low half) and addend C' (high half), each fp32 operation rounded on its
+// own in the order the format defines (sm120/ref15_spec.py:79-83, sm120/moe.py:130-132):
+//   A' = fp16(1.732421875 / Mb),  C' = fp16(((N / Mb) K0 + K0) - 1024 A'),  K0 = -3.453125, 1 / Mb rounded first.
+__device__ __forceinline__ uint32_t block_multipliers(uint32_t block_word)
+{
+    const float inv = __fdiv_rn(1.0f, (float)(block_word & 0xFFu));
+    const __half a = __float2half_rn(__fmul_rn(1.732421875f, inv));
+    const float ratio = __fmul_rn((float)((block_word >> 8) & 0xFFu), inv);
+    const float c = __fsub_rn(__fadd_rn(__fmul_rn(ratio, -3.453125f), -3.453125f), __fmul_rn(1024.0f, __half2float(a)));
+    return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(__float2half_rn(c)) << 16);
+}
+template <int SUM>
+__device__ __forceinline__ UnitConsts consts_level2(uint32_t sign2, const ByteSelect& sel)
 {
     UnitConsts k;
-    k.a2 = kMul1A2 ^ sign2; k.c2 = kMul1B2 ^ sign2; k.mrep = 0x01010101u; k.nrep = 0u;
+    k.a2 = kMul1A2 ^ sign2; k.c2 = kMul1B2 ^ sign2;
+    if constexpr (SUM == SUM_MMA) { k.m0 = sel.even & 0x01010101u; k.m1 = sel.odd & 0x01010101u; }
+    else { k.m0 = 0x01010101u; k.m1 = 0u; }
+    k.n0 = k.n1 = 0u;
     return k;
 }
-__device__ __forceinline__ UnitConsts consts_level4(uint32_t block_word, uint32_t sign2)
+// ac = block_multipliers(word), mbn = the block word
+template <int SUM>
+__device__ __forceinline__ UnitConsts consts_level4(uint32_t ac, uint32_t mbn, uint32_t sign2, const ByteSelect& sel)
 {
-    const uint32_t mb = block_word & 0xFFu, n = (block_word >> 8) & 0xFFu;
-    const float rc = __frcp_rn((float)mb);                                   // IEEE 1.0f / Mb
-    const __half ah = __float2half_rn(__fmul_rn(1.732421875f, rc));
-    const float t = __fadd_rn(__fmul_rn(__fmul_rn((float)n, rc), -3.453125f), -3.453125f);
-    const __half ch = __float2half_rn(__fsub_rn(t, __fmul_rn(1024.0f, __half2float(ah))));
     UnitConsts k;
-    k.a2 = ((uint32_t)__half_as_ushort(ah) * 0x00010001u) ^ sign2;
-    k.c2 = ((uint32_t)__half_as_ushort(ch) * 0x00010001u) ^ sign2;
-    k.mrep = mb * 0x01010101u; k.nrep = n * 0x01010101u;
+    k.a2 = __byte_perm(ac, 0u, 0x1010) ^ sign2; k.c2 = __byte_perm(ac, 0u, 0x3232) ^ sign2;
+    const uint32_t m = __byte_perm(mbn, 0u, 0x0000), n = __byte_perm(mbn, 0u, 0x1111);
+    if constexpr (SUM == SUM_MMA) { k.m0 = m & sel.even; k.m1 = m & sel.odd; k.n0 = n & sel.even; k.n1 = n & sel.odd; }
+    else { k.m0 = m; k.n0 = n; k.m1 = k.n1 = 0u; }
     return k;
 }
 
-// fp16x2 of lane weights 2 PP and 2 PP + 1.  RES: refined (level 4) unit, RC its residual window code, BK the window
-// code of the base stream (0 = 2 bits per weight in 128-bit records; 1 = 1.75 bits per weight in 112-bit records,
-// sm120/NQ_RES_V2.md:36-50: only the base state walk changes).
-template <bool RES, int RC, int PP, int BK = 0>
-__device__ __forceinline__ uint32_t decode_pair(const uint32_t* wb, const uint32_t* wr, const UnitConsts& k)
+// The A-fragment registers of k-step T: a[q] = rows g + 8 (q & 1), k = 16 T + 2 t4 + 8 (q >> 1) + {0, 1}, i.e.
+// a[q] = fp16x2 of lane weights 2 (4 T + q) and 2 (4 T + q) + 1.
+// RES: refined (level 4) unit, RC its residual window code, BK the window code of the base stream (0 = 2 bits per weight
+// in 128-bit records; 1 = 1.75 bits per weight in 112-bit records, sm120/NQ_RES_V2.md:36-50: only the base state walk
+// changes).  All 32 lanes must call it together when SUM == SUM_MMA.
+template <bool RES, int RC, int BK, int T, int SUM>
+__device__ __forceinline__ void decode_kstep(const uint32_t* wb, const uint32_t* wr, const UnitConsts& k, uint32_t (&a)[4])
 {
-    constexpr int b0 = step_offset(2 * PP, BK), b1 = step_offset(2 * PP + 1, BK);
-    const uint32_t x0 = window16<b0>(wb) * kHashMul, x1 = window16<b1>(wb) * kHashMul;
-    if constexpr (!RES)
+    // hashed base / residual word of lane weight 8 T + i
+    auto hb = [&](auto ic) { return state16<BK, 8 * T + decltype(ic)::value>(wb) * kHashMul; };
+    auto hr = [&](auto ic) { return state16<RC, 8 * T + decltype(ic)::value>(wr) * kHashMul; };
+    using std::integral_constant;
+    if constexpr (SUM == SUM_MMA)
     {
-        // 0x6400 + S is the fp16 bit pattern of 1024 + S (S <= 1020)
-        const uint32_t s0 = dot4(x0, 0x01010101u, 0x6400u), s1 = dot4(x1, 0x01010101u, 0x6400u);
-        return fma_h2(__byte_perm(s0, s1, 0x5410), k.a2, k.c2);
+        // one MMA per two fragment registers: A = {w(q, 0), w(q + 1, 0), w(q, 1), w(q + 1, 1)} -> d0, d1 = sums of
+        // pair q, d2, d3 = sums of pair q + 1
+        static_for<2>([&](auto hc) {
+            constexpr int q = 2 * decltype(hc)::value;
+            uint32_t d[4];
+            const uint32_t b0 = hb(integral_constant<int, 2 * q>{}), b1 = hb(integral_constant<int, 2 * q + 2>{});
+            const uint32_t b2 = hb(integral_constant<int, 2 * q + 1>{}), b3 = hb(integral_constant<int, 2 * q + 3>{});
+            if constexpr (!RES)
+            {
+                // 0x6400 + S is the fp16 bit pattern of 1024 + S (S <= 1020)
+                mma_bytes(d, b0, b1, b2, b3, k.m0, k.m1, 0x6400u, 0x6400u, 0x6400u, 0x6400u);
+                a[q] = fma_h2(__byte_perm(d[0], d[1], 0x5410), k.a2, k.c2);
+                a[q + 1] = fma_h2(__byte_perm(d[2], d[3], 0x5410), k.a2, k.c2);
+            }
+            else
+            {
+                // Mb Sb + N Sr + 128 + (0x6400 << 8): bits 8..23 are the fp16 pattern of 1024 + F
+                mma_bytes(d, b0, b1, b2, b3, k.m0, k.m1, 0x640080u, 0x640080u, 0x640080u, 0x640080u);
+                const uint32_t r0 = hr(integral_constant<int, 2 * q>{}), r1 = hr(integral_constant<int, 2 * q + 2>{});
+                const uint32_t r2 = hr(integral_constant<int, 2 * q + 1>{}), r3 = hr(integral_constant<int, 2 * q + 3>{});
+                mma_bytes(d, r0, r1, r2, r3, k.n0, k.n1, d[0], d[1], d[2], d[3]);
+                a[q] = fma_h2(__byte_perm(d[0], d[1], 0x6521), k.a2, k.c2);
+                a[q + 1] = fma_h2(__byte_perm(d[2], d[3], 0x6521), k.a2, k.c2);
+            }
+        });
     }
     else
     {
-        constexpr int o0 = step_offset(2 * PP, RC), o1 = step_offset(2 * PP + 1, RC);
-        // Mb Sb + N Sr + 128 + (0x6400 << 8): bits 8..23 are the fp16 pattern of 1024 + F
-        uint32_t t0 = dot4(x0, k.mrep, 0x640080u), t1 = dot4(x1, k.mrep, 0x640080u);
-        t0 = dot4(window16<o0>(wr) * kHashMul, k.nrep, t0);
-        t1 = dot4(window16<o1>(wr) * kHashMul, k.nrep, t1);
-        return fma_h2(__byte_perm(t0, t1, 0x6521), k.a2, k.c2);
+        static_for<4>([&](auto qc) {
+            constexpr int q = decltype(qc)::value;
+            if constexpr (!RES)
+            {
+                const uint32_t s0 = dot4(hb(integral_constant<int, 2 * q>{}), k.m0, 0x6400u);
+                const uint32_t s1 = dot4(hb(integral_constant<int, 2 * q + 1>{}), k.m0, 0x6400u);
+                a[q] = fma_h2(__byte_perm(s0, s1, 0x5410), k.a2, k.c2);
+            }
+            else
+            {
+                const uint32_t s0 = dot4(hr(integral_constant<int, 2 * q>{}), k.n0, dot4(hb(integral_constant<int, 2 * q>{}), k.m0, 0x640080u));
+                const uint32_t s1 = dot4(hr(integral_constant<int, 2 * q + 1>{}), k.n0, dot4(hb(integral_constant<int, 2 * q + 1>{}), k.m0, 0x640080u));
+                a[q] = fma_h2(__byte_perm(s0, s1, 0x6521), k.a2, k.c2);
+            }
+        });
     }
 }
 
-// ---------------------------------------------------------------- plane access
+// ---------------------------------------------------------------- plane pointers of one projection of one expert
 struct ProjPlanes
 {
     const uint4* base;        // 128-bit record per lane
@@ -183,62 +284,6 @@ __device__ __forceinline__ ProjPlanes planes_from_row(const int64_t* row, int do
     p.base = (const uint4*)row[o]; p.p4 = (const uint8_t*)row[o + 1]; p.d4 = (const uint32_t*)row[o + 2];
     p.flags = (const uint64_t*)row[o + 3]; p.var = (const uint8_t*)row[down ? 13 : 12];
     return p;
-}
-
-__device__ __forceinline__ uint4 ldg_stream128(const void* p)
-{
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint2 ldg_stream64(const void* p)
-{
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint32_t ldg_stream32(const void* p)
-{
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint32_t ldg_stream16(const void* p)
-{
-    uint16_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
-    return v;
-}
-
-// words of record `rec` of a residual plane of `nrec` records (sub-arrays: 128-bit pieces record-major, then a
-// 64-, 32-, 16-bit piece per record, then a bit-packed tail of BITS % 16 bits per record followed by a 4-byte pad)
-template <int BITS>
-__device__ __forceinline__ void load_record(uint32_t* w, const uint8_t* __restrict__ p, size_t rec, size_t nrec)
-{
-    constexpr int n4 = BITS / 128, rem = BITS % 128, T = BITS % 16;
-    int k = 0;
-#pragma unroll
-    for (int i = 0; i < n4; ++i)
-    {
-        const uint4 v = ldg_stream128(p + (rec * n4 + i) * 16);
-        w[k++] = v.x; w[k++] = v.y; w[k++] = v.z; w[k++] = v.w;
-    }
-    p += nrec * 16 * (size_t)n4;
-    if constexpr ((rem & 64) != 0) { const uint2 v = ldg_stream64(p + rec * 8); w[k++] = v.x; w[k++] = v.y; p += nrec * 8; }
-    if constexpr ((rem & 32) != 0) { w[k++] = ldg_stream32(p + rec * 4); p += nrec * 4; }
-    if constexpr ((rem & 16) != 0) { w[k++] = ldg_stream16(p + rec * 2); p += nrec * 2; }
-    if constexpr (T != 0)
-    {
-        const size_t bit = rec * T;
-        const uint8_t* q = p + (bit >> 5) * 4;
-        const int sh = (int)(bit & 31);
-        uint32_t v;
-        if constexpr ((32 % T) != 0) v = __funnelshift_r(ldg_stream32(q), ldg_stream32(q + 4), sh);   // second word: next record word or the pad
-        else v = ldg_stream32(q) >> sh;
-        v &= (1u << T) - 1u;
-        if constexpr (((BITS - T) & 31) == 16) w[k - 1] |= v << 16;
-        else w[k++] = v;
-    }
 }
 
 }  // namespace nq

@@ -6,7 +6,8 @@
 
 namespace nq {
 
-constexpr int kTileStride = 68;   // 32-bit words per tile row: 64 + 4 pad (16-byte aligned rows, conflict-free fragment stores)
+constexpr int kTileStride = 68;   // 32-bit words per tile row: 64 + 4 pad keeps rows 16-byte aligned and spreads the 8 rows a fragment
+                                  // store touches over all banks
 
 struct TileSink
 {
@@ -19,12 +20,43 @@ struct TileSink
     }
 };
 
-// grid (ceil(max_units / 8), n_experts, 2 = gate|up / down), 256 threads
+// fetch the unit's records into the warp's stage, read them back and decode
+template <bool RES, int RC, int BK>
+__device__ __forceinline__ void decode_one(const ProjPlanes& P, const StripRef& sr, int ch, int C, int NS, uint32_t sign2, int lane,
+                                           uint8_t* st, const TileSink& sink)
+{
+    const ByteSelect sel = byte_select(lane);
+    RecordCursor<BK> cb;
+    cb.init(P.base, (size_t)NS * C * 32, sr.unit0 + ch, lane);
+    cb.copy(st, 0, lane);
+    uint32_t wb[Pattern<BK>::kWords + 2], wr[Pattern<RC>::kWords + 2];
+    if constexpr (RES)
+    {
+        RecordCursor<RC> cr;
+        cr.init(P.p4, sr.res_nrec, sr.res0 + refined_before(sr, ch), lane);
+        cr.copy(st + kStageBase, 0, lane);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    RecordCursor<BK>::read(wb, st, lane);
+    if constexpr (RES)
+    {
+        RecordCursor<RC>::read(wr, st + kStageBase, lane);
+        const uint32_t word = __ldg(P.d4 + sr.res0 + refined_before(sr, ch));
+        decode_unit<true, RC, BK, kSumDefault>(wb, wr, consts_level4<kSumDefault>(block_multipliers(word), word, sign2, sel), lane, sink);
+    }
+    else
+        decode_unit<false, 0, BK, kSumDefault>(wb, wr, consts_level2<kSumDefault>(sign2, sel), lane, sink);
+}
+
+// grid (ceil(max_units / 8), n_experts, 2 = gate|up / down), 256 threads.  The records take the same road as in the
+// GEMV and the fused GEMM (cp.async into a per-warp stage, read back by the lane that copied them).
 __global__ void __launch_bounds__(256) pf_decode_kernel(const int64_t* __restrict__ table, const int32_t* __restrict__ experts,
                                                         __half* Wgu, __half* Wdn, int H, int I, int nm_gu, int nm_dn,
                                                         int force_level)
 {
     __shared__ __align__(16) uint32_t tiles[8][16 * kTileStride];
+    __shared__ __align__(16) uint8_t stages[8][kStageBytes];
     const int down = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __half* Wout = down ? Wdn : Wgu;
     if (!Wout) return;
@@ -36,6 +68,7 @@ __global__ void __launch_bounds__(256) pf_decode_kernel(const int64_t* __restric
     int level = (int)row[0];
     if (force_level > 0 && level > 0) level = force_level;
     uint32_t* tile = tiles[warp];
+    uint8_t* st = stages[warp];
     Wout += (size_t)blockIdx.y * N * K + (size_t)strip * 16 * K + (size_t)ch * 128;
     if (level <= 0)
     {
@@ -44,8 +77,13 @@ __global__ void __launch_bounds__(256) pf_decode_kernel(const int64_t* __restric
     }
     const ProjPlanes P = planes_from_row(row, down);
     const int nm = down ? nm_dn : nm_gu, rc = (int)row[10 + down], bk = (int)(row[19] >> (8 * down)) & 0xFF;
-    const UnitRef u = locate_unit(P, strip, ch, C, NS, nm, level);
-    decode_unit_dispatch(P, u, rc, bk, lane, TileSink{tile, lane >> 2, lane & 3});
+    const StripRef sr = locate_strip(P, strip, C, NS, nm, level >= 4);
+    const bool refined = chunk_refined(sr, ch);
+    const uint32_t sign2 = P.var ? sign_mask(__ldg(P.var + sr.unit0 + ch), lane) : 0u;
+    const TileSink sink{tile, lane >> 2, lane & 3};
+#define NQ_RUN(RES, RCV, BKV) decode_one<RES, RCV, BKV>(P, sr, ch, C, NS, sign2, lane, st, sink)
+    NQ_WITH_CODES(refined, rc, bk, 0x3FF, NQ_RUN);
+#undef NQ_RUN
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 8; ++j)

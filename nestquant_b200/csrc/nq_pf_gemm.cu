@@ -24,16 +24,10 @@
 #include <cuda.h>
 
 #include "nq_common.cuh"
-#include "nq_stream.cuh"
 #include "nq_unit.cuh"
 
 namespace nq {
 
-// timing experiments only (results are then wrong): 1 = decode warps skip the decode, 2 = no MMAs are issued, 3 = no
-// MMAs and no token-tile loads, 4 = as 1 with half of each token tile loaded, 5 = everything runs, half of each tile loaded
-#ifndef NQ_PF_DEBUG
-#define NQ_PF_DEBUG 0
-#endif
 #ifndef NQ_PF_SPLIT
 #define NQ_PF_SPLIT 256      // token tiles wider than this are multiplied as two column halves
 #endif
@@ -41,6 +35,10 @@ namespace nq {
 #define NQ_PF_GROUPS 2      // groups of 8 decode warps; group g takes the chunks c = g (mod groups) of its strips.  3 groups
                             // (24 decode warps at 72 registers) measured the same time as 2: the kernel runs at the power cap
 #endif
+#ifndef NQ_PF_SUM
+#define NQ_PF_SUM NQ_SUM    // how the decode warps add hash bytes (see nq_format.cuh)
+#endif
+constexpr int kPfSum = NQ_PF_SUM;
 constexpr int kPfGroups = NQ_PF_GROUPS;
 constexpr int kPfDecodeWarps = 8 * kPfGroups;
 constexpr int kPfAStages = 2 * kPfGroups;            // weight tiles in tensor memory: each unit fills two consecutive stages
@@ -280,16 +278,10 @@ struct UnitSink
 // One decode warp, one item: its strip over the chunks c = GROUP, GROUP + 2, ... (the other group of 8 warps takes the
 // other parity), i.e. k-blocks 4 i + 2 GROUP and + 1.  it_base = k-blocks of earlier items.  false = aborted.
 template <bool REFINED, int RC, int BK, class Mid>
-__device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int C, int NS, int nm, int lane, int group,
+__device__ __forceinline__ bool decode_strip(const ProjPlanes& P, const StripRef& sr, int C, int NS, int lane, int group,
                                              uint32_t tmem_a, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
 {
-    unsigned long long fl = ~0ull;
-    if (REFINED && P.flags) fl = __ldg((const unsigned long long*)P.flags + strip);
-    const size_t res_nrec = (size_t)NS * (P.flags ? nm : C) * 32;
-    const size_t unit0 = (size_t)strip * C;
-    auto res_unit = [&](int ch) -> size_t {
-        return P.flags ? (size_t)strip * nm + __popcll(fl & ((1ull << ch) - 1ull)) : unit0 + ch;
-    };
+    const ByteSelect sel = byte_select(lane);
     // per-unit scalars of this warp's chunks, one chunk (group + kPfGroups * lane) per lane: ring signs and, for refined units,
     // the block word with its fp16 multiplier / addend (computed once here instead of by every lane of every unit)
     uint32_t var_b = 0, ac = 0, mbn = 0;
@@ -297,20 +289,23 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
         const int ch = group + kPfGroups * lane;
         if (ch < C)
         {
-            if (P.var) var_b = __ldg(P.var + unit0 + ch);
+            if (P.var) var_b = __ldg(P.var + sr.unit0 + ch);
             if constexpr (REFINED)
-                if ((fl >> ch) & 1ull)
+                if (chunk_refined(sr, ch))
                 {
-                    mbn = __ldg(P.d4 + res_unit(ch)) & 0xFFFFu;
-                    const UnitConsts k = consts_level4(mbn, 0u);
-                    ac = (k.a2 & 0xFFFFu) | (k.c2 << 16);
+                    mbn = __ldg(P.d4 + sr.res0 + refined_before(sr, ch)) & 0xFFFFu;
+                    ac = block_multipliers(mbn);
                 }
         }
     }
+    RecordCursor<BK> cb;
+    cb.init(P.base, (size_t)NS * C * 32, sr.unit0, lane);
+    RecordCursor<RC> cr;
+    if constexpr (REFINED) cr.init(P.p4, sr.res_nrec, sr.res0, lane);
     auto issue = [&](int ch, uint8_t* st) {
-        copy_base<BK>(st, P.base, (unit0 + ch) * 32 + lane, (size_t)NS * C * 32, lane);
+        cb.copy(st, ch, lane);
         if constexpr (REFINED)
-            if ((fl >> ch) & 1ull) copy_record<RC>(st + 512, P.p4, res_unit(ch) * 32 + lane, res_nrec, lane);
+            if (chunk_refined(sr, ch)) cr.copy(st + kStageBase, refined_before(sr, ch), lane);
     };
 #pragma unroll
     for (int d = 0; d < kPfRingDepth - 1; ++d)
@@ -328,37 +323,20 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, int strip, int
         const uint8_t* st = ring + slot * kStageBytes;
         slot = slot + 1 == kPfRingDepth ? 0 : slot + 1;
         slot_in = slot_in + 1 == kPfRingDepth ? 0 : slot_in + 1;
-        const uint32_t vb = __shfl_sync(0xffffffffu, var_b, i);
-        const uint32_t sign2 = ((vb >> (lane >> 2)) & 1u) * 0x80008000u;
-        uint32_t wb[Pattern<BK>::kWords + 2];
-        read_base<BK>(wb, st, (unit0 + ch) * 32 + lane, lane);
+        const uint32_t sign2 = sign_mask(__shfl_sync(0xffffffffu, var_b, i), lane);
+        uint32_t wb[Pattern<BK>::kWords + 2], wr[Pattern<RC>::kWords + 2];
+        RecordCursor<BK>::read(wb, st, lane);
         const UnitSink sink{tmem_a, sh, it_base + 2 * (uint32_t)ch, lane, &ok};
         bool refined = false;
-        if constexpr (REFINED) refined = (fl >> ch) & 1ull;
-#if NQ_PF_DEBUG == 1 || NQ_PF_DEBUG == 4
-        if (ok)
-            for (int hh = 0; hh < 2; ++hh)
-            {
-                const uint32_t it = it_base + 2 * ch + hh, sa = it % kPfAStages;
-                if (!mbar_wait(&sh->empty_a[sa], ((it / kPfAStages) & 1u) ^ 1u, &sh->abort_flag)) { ok = false; break; }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sh->full_a[sa]);
-            }
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-#else
+        if constexpr (REFINED) refined = chunk_refined(sr, ch);
         if (refined)
         {
             const uint32_t acw = __shfl_sync(0xffffffffu, ac, i), mb = __shfl_sync(0xffffffffu, mbn, i);
-            UnitConsts k;
-            k.a2 = __byte_perm(acw, 0u, 0x1010) ^ sign2; k.c2 = __byte_perm(acw, 0u, 0x3232) ^ sign2;
-            k.mrep = __byte_perm(mb, 0u, 0x0000); k.nrep = __byte_perm(mb, 0u, 0x1111);
-            uint32_t wr[Pattern<RC>::kWords + 2];
-            read_record<RC>(wr, st + 512, res_unit(ch) * 32 + lane, lane);
-            decode_words<true, RC, BK>(wb, wr, k, lane, sink);
+            RecordCursor<RC>::read(wr, st + kStageBase, lane);
+            decode_unit<true, RC, BK, kPfSum>(wb, wr, consts_level4<kPfSum>(acw, mb, sign2, sel), lane, sink);
         }
         else
-            decode_words<false, 0, BK>(wb, nullptr, consts_level2(sign2), lane, sink);
-#endif
+            decode_unit<false, 0, BK, kPfSum>(wb, wr, consts_level2<kPfSum>(sign2, sel), lane, sink);
         if (i == 0) mid();      // the previous item's epilogue, once this item's first tiles are on their way
     }
     cp_async_wait<0>();
@@ -369,30 +347,12 @@ template <class Mid>
 __device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int rc, int bk, int strip, int C, int NS, int nm, int lane, int group,
                                             uint32_t tmem_a, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
 {
-#define NQ_RUN(REF, RCV) return decode_strip<REF, RCV, 0>(P, strip, C, NS, nm, lane, group, tmem_a, ring, sh, it_base, mid)
-#define NQ_RUN1(REF, RCV) return decode_strip<REF, RCV, 1>(P, strip, C, NS, nm, lane, group, tmem_a, ring, sh, it_base, mid)
-    if (bk == 1)        // 112-bit base records, with the residual codes they ship with
-    {
-        if (level < 4) NQ_RUN1(false, 0);
-        if (rc == 9) NQ_RUN1(true, 9);
-        NQ_RUN1(true, 3);
-    }
-    if (level < 4) NQ_RUN(false, 0);
-    switch (rc)
-    {
-        case 1: NQ_RUN(true, 1);
-        case 2: NQ_RUN(true, 2);
-        case 3: NQ_RUN(true, 3);
-        case 4: NQ_RUN(true, 4);
-        case 5: NQ_RUN(true, 5);
-        case 6: NQ_RUN(true, 6);
-        case 7: NQ_RUN(true, 7);
-        case 8: NQ_RUN(true, 8);
-        case 9: NQ_RUN(true, 9);
-        default: NQ_RUN(true, 0);
-    }
+    const StripRef sr = locate_strip(P, strip, C, NS, nm, level >= 4);
+    bool ok = true;
+#define NQ_RUN(REF, RCV, BKV) ok = decode_strip<REF, RCV, BKV>(P, sr, C, NS, lane, group, tmem_a, ring, sh, it_base, mid)
+    NQ_WITH_CODES(level >= 4, rc, bk, 0x3FF, NQ_RUN);
 #undef NQ_RUN
-#undef NQ_RUN1
+    return ok;
 }
 
 // grid = resident CTAs (one per SM), 576 threads
@@ -478,14 +438,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             {
                 if (!mbar_wait_warp(&sh->empty_b[s], ((par_b >> s) & 1u) ^ 1u, &sh->abort_flag)) break;
                 par_b ^= 1u << s;
-#if NQ_PF_DEBUG == 3
-                mbar_arrive_elect(&sh->full_b[s]);
-#else
-                const int nld = NQ_PF_DEBUG >= 4 ? (nbox + 1) / 2 : nbox;
-                mbar_expect_tx_elect(&sh->full_b[s], (uint32_t)nld * kPfBoxBytes);
-                for (int j = 0; j < nld; ++j)
+                mbar_expect_tx_elect(&sh->full_b[s], (uint32_t)nbox * kPfBoxBytes);
+                for (int j = 0; j < nbox; ++j)
                     tma_load_2d_elect(b_tiles + (s * sbox + j) * kPfBoxBytes, map, kb * 64, ps.row0 + j * kPfBoxRows, &sh->full_b[s]);
-#endif
             }
         }
         else if (warp == 1)
@@ -507,11 +462,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
                     !mbar_wait_warp(&sh->full_a[sa], (it / kPfAStages) & 1u, &sh->abort_flag)) { ok = false; break; }
                 par_b ^= 1u << s;
                 tc_fence_after();
-#if NQ_PF_DEBUG != 2 && NQ_PF_DEBUG != 3
                 const uint32_t ta = tmem + kPfAccCols + sa * kPfACols;
                 if (n1 > 0) tc_mma_kblock2(tmem, tmem + n0, ta, b_lo, b_lo + (uint32_t)(n0 * 8), b_hi, idesc0, idesc1, (uint32_t)kb);
                 else tc_mma_kblock(tmem, ta, b_lo, b_hi, idesc0, (uint32_t)kb);
-#endif
                 tc_commit_elect(&sh->empty_a[sa]);       // both arrive when the MMAs above have read their operands
                 tc_commit_elect(&sh->empty_b[s]);
                 if (++s == (uint32_t)nb) { s = 0; b_lo = b_lo0; } else b_lo += b_step;
@@ -619,16 +572,19 @@ int nq_pf_gemm(const int64_t* table, const int32_t* plan, const void* act0, cons
     NQ_REQUIRE(pairs >= 0, "nq_pf_gemm: pairs = %d", pairs);
     if (pairs == 0) return NQ_OK;
     NQ_REQUIRE(nq::aligned16(act0) && nq::aligned16(act1) && nq::aligned16(out0), "nq_pf_gemm: matrices must be 16-byte aligned");
-    static int ctas = 0;
-    if (!ctas)
+    // SM count and the shared-memory opt-in are per device: cached per device ordinal
+    static int ctas_of[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nq::fail(NQ_ERR_CUDA, "nq_pf_gemm: no usable current device");
+    if (!ctas_of[dev])
     {
-        int dev = 0, sms = 0;
-        cudaGetDevice(&dev);
+        int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (cudaFuncSetAttribute((const void*)nq::pf_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, nq::kPfSmem) != cudaSuccess)
             return nq::fail(NQ_ERR_CUDA, "nq_pf_gemm: cannot reserve %d bytes of shared memory", nq::kPfSmem);
-        ctas = sms;
+        ctas_of[dev] = sms;
     }
+    const int ctas = ctas_of[dev];
     CUtensorMap m0, m1;
     const size_t K = down ? I : H;
     if (int e = nq::make_tile_map(&m0, act0, (size_t)pairs, K)) return e;

@@ -47,9 +47,10 @@ __device__ __forceinline__ float quad_sum(float d)
 }
 // one CTA per pair, one warp per 1024 columns
 __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(const __half* __restrict__ x, const int* __restrict__ pt, const int* __restrict__ pe,
-                                                     const int64_t* __restrict__ table, __half* xg, __half* xu, float* zg, int H, int I, int kperm)
+                                                     const int64_t* __restrict__ table, int E, __half* xg, __half* xu, float* zg, int H, int I, int kperm)
 {
     const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (pe[p] < 0 || pe[p] >= E) return;      // a pick with no valid expert id (padding): nothing to prepare
     const int64_t* row = table + (int64_t)pe[p] * kTableWidth;
     const int level = (int)row[0];
     if (level <= 0) return;
@@ -96,11 +97,12 @@ __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(const __ha
 
 // one CTA per pair, one warp per 1024 columns; dynamic shared memory: I floats (staging for the 512-wide rotation)
 __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_mid_kernel(const float* __restrict__ acc_g, const float* __restrict__ acc_u, const float* __restrict__ zg,
-                                                     const int* __restrict__ pe, const int64_t* __restrict__ table, __half* h, float* zd, int H, int I, int kperm)
+                                                     const int* __restrict__ pe, const int64_t* __restrict__ table, int E, __half* h, float* zd, int H, int I, int kperm)
 {
     extern __shared__ float stage[];
     __shared__ float zpart[64][4];
     const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5, ng = I / 128;
+    if (pe[p] < 0 || pe[p] >= E) return;
     const int64_t* row = table + (int64_t)pe[p] * kTableWidth;
     const int level = (int)row[0];
     if (level <= 0) return;
@@ -221,9 +223,10 @@ __device__ __forceinline__ bool pair_output(const float* __restrict__ y, const f
 // one CTA per pair: atomic accumulation into out[token]
 __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_post_kernel(const float* __restrict__ y, const float* __restrict__ zd, const int* __restrict__ pt,
                                                       const int* __restrict__ pe, const __half* __restrict__ prw,
-                                                      const int64_t* __restrict__ table, float* out, int H, int I)
+                                                      const int64_t* __restrict__ table, int E, float* out, int H, int I)
 {
     const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5, ng = H / 128;
+    if (pe[p] < 0 || pe[p] >= E) return;
     const float w = __half2float(prw[p]);
     float* op = out + (size_t)pt[p] * H;
     for (int g0 = warp * 8; g0 < ng; g0 += nwarp * 8)
@@ -238,26 +241,40 @@ __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_post_kernel(const flo
     }
 }
 
-// one CTA per token: picks added in pick order, out written once.  pos[t * topk + k] = index of that pick in the
-// expert-sorted pair arrays.
+// one CTA per token: the token's picks whose pairs lie in [pair0, pair0 + npairs) are added in pick order.  pos[t * topk + k] =
+// index of that pick in the expert-sorted pair list; y / zd hold the rows of that window only (row = index - pair0).
+// accumulate = 0: out[t] is overwritten (zeros if the token has no pick in the window); 1: the sum is added to out[t], and
+// tokens without a pick in the window are not touched.  Calling it window after window in a fixed order gives a bitwise
+// repeatable result without a pairs-sized buffer.
 __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_combine_kernel(const float* __restrict__ y, const float* __restrict__ zd, const int* __restrict__ pos,
                                                          const int64_t* __restrict__ sel, const __half* __restrict__ rw,
-                                                         const int64_t* __restrict__ table, float* out, int topk, int E, int H, int I)
+                                                         const int64_t* __restrict__ table, float* out, int topk, int E, int H, int I,
+                                                         int pair0, int npairs, int accumulate)
 {
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5, ng = H / 128;
+    bool any = false;
+    for (int k = 0; k < topk; ++k)
+    {
+        const int p = pos[(size_t)t * topk + k] - pair0;
+        any = any || (p >= 0 && p < npairs);
+    }
+    if (accumulate && !any) return;      // CTA-uniform
     for (int g0 = warp * 8; g0 < ng; g0 += nwarp * 8)
     {
         const int grp = g0 + (lane >> 2), col = grp * 128;
         const bool live = grp < ng;
         float o[32];
+        if (accumulate && live) load32f_mapF(out + (size_t)t * H + col, lane & 3, o);
+        else
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = 0.f;
+            for (int i = 0; i < 32; ++i) o[i] = 0.f;
         for (int k = 0; k < topk; ++k)
         {
             const int64_t e = sel[(size_t)t * topk + k];
-            if (e < 0 || e >= E) continue;
+            const int p = pos[(size_t)t * topk + k] - pair0;
+            if (e < 0 || e >= E || p < 0 || p >= npairs) continue;
             float v[32];
-            if (!pair_output(y, zd, pos[(size_t)t * topk + k], (int)e, __half2float(rw[(size_t)t * topk + k]), table, H, I, col, live, lane, v))
+            if (!pair_output(y, zd, p, (int)e, __half2float(rw[(size_t)t * topk + k]), table, H, I, col, live, lane, v))
                 continue;
             if (live)
 #pragma unroll
@@ -282,51 +299,55 @@ extern "C" {
 
 #define NQ_SHAPE_OK(fn) NQ_REQUIRE(H > 0 && I > 0 && H % 128 == 0 && I % 128 == 0 && H / 128 <= 64 && I / 128 <= 64, fn ": H = %d, I = %d must be multiples of 128, at most 64 * 128", H, I)
 
-int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const int64_t* table, void* xg, void* xu, float* zg,
+int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const int64_t* table, int E, void* xg, void* xu, float* zg,
               int H, int I, int kperm, void* stream)
 {
     NQ_REQUIRE(R >= 0, "nq_pf_pre: R = %d", R);
     if (R == 0) return NQ_OK;
     NQ_REQUIRE(x && pt && pe && table && xg && xu && zg, "nq_pf_pre: null pointer");
     NQ_SHAPE_OK("nq_pf_pre");
+    NQ_REQUIRE(E >= 1, "nq_pf_pre: E = %d", E);
     NQ_REQUIRE(nq::aligned16(x) && nq::aligned16(xg) && nq::aligned16(xu), "nq_pf_pre: x, xg, xu must be 16-byte aligned");
-    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>((const __half*)x, pt, pe, table, (__half*)xg, (__half*)xu, zg, H, I, kperm);
+    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>((const __half*)x, pt, pe, table, E, (__half*)xg, (__half*)xu, zg, H, I, kperm);
     return nq::check_launch("nq_pf_pre");
 }
 
-int nq_pf_mid(const float* acc_g, const float* acc_u, const float* zg, const int32_t* pe, int R, const int64_t* table, void* h,
+int nq_pf_mid(const float* acc_g, const float* acc_u, const float* zg, const int32_t* pe, int R, const int64_t* table, int E, void* h,
               float* zd, int H, int I, int kperm, void* stream)
 {
     NQ_REQUIRE(R >= 0, "nq_pf_mid: R = %d", R);
     if (R == 0) return NQ_OK;
     NQ_REQUIRE(acc_g && acc_u && zg && pe && table && h && zd, "nq_pf_mid: null pointer");
     NQ_SHAPE_OK("nq_pf_mid");
+    NQ_REQUIRE(E >= 1, "nq_pf_mid: E = %d", E);
     NQ_REQUIRE(nq::aligned16(acc_g) && nq::aligned16(acc_u) && nq::aligned16(h), "nq_pf_mid: acc_g, acc_u, h must be 16-byte aligned");
-    nq::pf_mid_kernel<<<R, nq::pf_threads(I), (size_t)I * 4, (cudaStream_t)stream>>>(acc_g, acc_u, zg, pe, table, (__half*)h, zd, H, I, kperm);
+    nq::pf_mid_kernel<<<R, nq::pf_threads(I), (size_t)I * 4, (cudaStream_t)stream>>>(acc_g, acc_u, zg, pe, table, E, (__half*)h, zd, H, I, kperm);
     return nq::check_launch("nq_pf_mid");
 }
 
-int nq_pf_post(const float* y, const float* zd, const int32_t* pt, const int32_t* pe, const void* prw, int R, const int64_t* table,
+int nq_pf_post(const float* y, const float* zd, const int32_t* pt, const int32_t* pe, const void* prw, int R, const int64_t* table, int E,
                float* out, int H, int I, void* stream)
 {
     NQ_REQUIRE(R >= 0, "nq_pf_post: R = %d", R);
     if (R == 0) return NQ_OK;
     NQ_REQUIRE(y && zd && pt && pe && prw && table && out, "nq_pf_post: null pointer");
     NQ_SHAPE_OK("nq_pf_post");
+    NQ_REQUIRE(E >= 1, "nq_pf_post: E = %d", E);
     NQ_REQUIRE(nq::aligned16(y) && nq::aligned16(out), "nq_pf_post: y and out must be 16-byte aligned");
-    nq::pf_post_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>(y, zd, pt, pe, (const __half*)prw, table, out, H, I);
+    nq::pf_post_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>(y, zd, pt, pe, (const __half*)prw, table, E, out, H, I);
     return nq::check_launch("nq_pf_post");
 }
 
 int nq_pf_combine(const float* y, const float* zd, const int32_t* pos, const int64_t* sel, const void* rw, int T, int topk,
-                  const int64_t* table, int E, float* out, int H, int I, void* stream)
+                  const int64_t* table, int E, float* out, int H, int I, int pair0, int npairs, int accumulate, void* stream)
 {
     NQ_REQUIRE(T >= 0 && topk >= 1 && E >= 1, "nq_pf_combine: T = %d, topk = %d, E = %d", T, topk, E);
+    NQ_REQUIRE(pair0 >= 0 && npairs >= 0, "nq_pf_combine: pair window %d + %d", pair0, npairs);
     if (T == 0) return NQ_OK;
     NQ_REQUIRE(y && zd && pos && sel && rw && table && out, "nq_pf_combine: null pointer");
     NQ_SHAPE_OK("nq_pf_combine");
     NQ_REQUIRE(nq::aligned16(y) && nq::aligned16(out), "nq_pf_combine: y and out must be 16-byte aligned");
-    nq::pf_combine_kernel<<<T, nq::pf_threads(H), 0, (cudaStream_t)stream>>>(y, zd, pos, sel, (const __half*)rw, table, out, topk, E, H, I);
+    nq::pf_combine_kernel<<<T, nq::pf_threads(H), 0, (cudaStream_t)stream>>>(y, zd, pos, sel, (const __half*)rw, table, out, topk, E, H, I, pair0, npairs, accumulate);
     return nq::check_launch("nq_pf_combine");
 }
 

@@ -1,13 +1,22 @@
-// Asynchronous stream of packed planes into shared memory, shared by the decode-path GEMV and the prefill GEMM.
+// Asynchronous stream of packed planes into shared memory, shared by the decode-path GEMV, the prefill GEMM and the dense
+// decode kernel.
+//
+// Plane layout (sm120/moe.py:36-49): a record of BITS bits is cut into pieces - BITS / 128 pieces of 128 bits, then a
+// 64-, a 32- and a 16-bit piece as the binary digits of BITS % 128 say, then a tail of BITS % 16 bits - and every piece
+// kind is stored as its own array over all records of the plane (the tail bit-packed, followed by a 4-byte pad).  The
+// base plane of window code 0 is the special case of one 128-bit piece.
+//
+// Each lane copies the pieces of its own record with cp.async (global -> shared, no registers) a few units ahead and
+// later reads back only what it copied itself, so the ring needs no barrier at all.  Per warp and stage: 512 B for the
+// base records of a unit followed by 768 B for its residual records, one lane-indexed array per piece kind.
+// 32 records make a unit, so every piece array advances by a fixed number of bytes per unit and a lane's position
+// inside its unit's share of each array never changes: a cursor keeps one pointer per piece kind.
 #pragma once
 #include "nq_format.cuh"
 
 namespace nq {
 
-// Each lane copies the words of its own records with cp.async (global -> shared, no registers) a few units ahead and
-// later reads back only what it copied itself, so the ring needs no barrier at all.  Per warp and stage:
-// 512 B of base records followed by the residual pieces of the unit, one lane-indexed array per piece.
-constexpr int kStageBytes = 512 + 768;   // base + the widest residual layout (see ResidualSlots)
+constexpr int kStageBase = 512, kStageBytes = kStageBase + 768;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src)
 {
@@ -25,86 +34,73 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// byte offsets, inside the residual part of a stage, of each piece of a record of window code RC
-template <int RC>
-struct ResidualSlots
+// pieces of a record of window code CODE and where they sit inside a stage part
+template <int CODE>
+struct RecordLayout
 {
-    static constexpr int kBits = Pattern<RC>::kBits;
-    static constexpr int n4 = kBits / 128, rem = kBits % 128, T = kBits % 16;
+    static constexpr int kBits = Pattern<CODE>::kBits;
+    static constexpr int n128 = kBits / 128, rem = kBits % 128, T = kBits % 16;
     static constexpr bool has64 = (rem & 64) != 0, has32 = (rem & 32) != 0, has16 = (rem & 16) != 0;
-    static constexpr bool tail2 = T != 0 && (32 % T) != 0;          // a tail that can straddle two words
-    static constexpr int o128 = 0, o64 = o128 + 512 * n4, o32 = o64 + (has64 ? 256 : 0), o16 = o32 + (has32 ? 128 : 0);
+    static constexpr bool tail2 = T != 0 && (32 % (T ? T : 1)) != 0;          // a lane's tail can straddle two words
+    static constexpr int o128 = 0, o64 = o128 + 512 * n128, o32 = o64 + (has64 ? 256 : 0), o16 = o32 + (has32 ? 128 : 0);
     static constexpr int otail = o16 + (has16 ? 128 : 0), end = otail + (T ? (tail2 ? 256 : 128) : 0);
-    static_assert(n4 <= 1 && end <= kStageBytes - 512, "stage too small for this window code");
+    static_assert(n128 <= 1 && end <= kStageBytes - kStageBase, "stage too small for this window code");
+    // the tail lands in the upper half of the 16-bit piece's word when the pieces before it end on a half word
+    static constexpr bool tail_joins = T != 0 && ((kBits - T) & 31) == 16;
 };
 
-// enqueue the copies of record `rec` (= refined unit * 32 + lane) of a residual plane of `nrec` records
-template <int RC>
-__device__ __forceinline__ void copy_record(uint8_t* st, const uint8_t* __restrict__ p, size_t rec, size_t nrec, int lane)
+// One lane's read position in a plane of `nrec` records, at unit `unit0`; copy(stage, u) fetches unit unit0 + u.
+template <int CODE>
+struct RecordCursor
 {
-    using L = ResidualSlots<RC>;
-    if constexpr (L::n4) { cp_async16(st + L::o128 + lane * 16, p + rec * 16); p += nrec * 16; }
-    if constexpr (L::has64) { cp_async8(st + L::o64 + lane * 8, p + rec * 8); p += nrec * 8; }
-    if constexpr (L::has32) { cp_async4(st + L::o32 + lane * 4, p + rec * 4); p += nrec * 4; }
-    if constexpr (L::has16) { cp_async4(st + L::o16 + lane * 4, p + ((rec * 2) & ~(size_t)3)); p += nrec * 2; }
-    if constexpr (L::T != 0)
-    {
-        const uint8_t* q = p + ((rec * L::T) >> 5) * 4;
-        if constexpr (L::tail2) { cp_async4(st + L::otail + lane * 8, q); cp_async4(st + L::otail + lane * 8 + 4, q + 4); }
-        else cp_async4(st + L::otail + lane * 4, q);
-    }
-}
-// read the record back as stream words w[0 .. kWords)
-template <int RC>
-__device__ __forceinline__ void read_record(uint32_t* w, const uint8_t* st, size_t rec, int lane)
-{
-    using L = ResidualSlots<RC>;
-    int k = 0;
-    if constexpr (L::n4) { const uint4 v = *(const uint4*)(st + L::o128 + lane * 16); w[k++] = v.x; w[k++] = v.y; w[k++] = v.z; w[k++] = v.w; }
-    if constexpr (L::has64) { const uint2 v = *(const uint2*)(st + L::o64 + lane * 8); w[k++] = v.x; w[k++] = v.y; }
-    if constexpr (L::has32) w[k++] = *(const uint32_t*)(st + L::o32 + lane * 4);
-    if constexpr (L::has16)
-    {
-        const uint32_t v = *(const uint32_t*)(st + L::o16 + lane * 4);
-        w[k++] = (rec & 1) ? v >> 16 : v & 0xFFFFu;
-    }
-    if constexpr (L::T != 0)
-    {
-        const int sh = (int)((rec * L::T) & 31);
-        uint32_t v;
-        if constexpr (L::tail2)
-        {
-            const uint2 t = *(const uint2*)(st + L::otail + lane * 8);
-            v = __funnelshift_r(t.x, t.y, sh);
-        }
-        else v = *(const uint32_t*)(st + L::otail + lane * 4) >> sh;
-        v &= (1u << L::T) - 1u;
-        if constexpr (((L::kBits - L::T) & 31) == 16) w[k - 1] |= v << 16;
-        else w[k++] = v;
-    }
-}
+    using L = RecordLayout<CODE>;
+    const uint8_t *p128, *p64, *p32, *p16, *ptail;
 
-// base records of a unit in the first 512 bytes of a stage: one 16-byte copy per lane for base code 0, the sub-array
-// pieces (same slot layout as a residual record) for the others
-template <int BK>
-__device__ __forceinline__ void copy_base(uint8_t* st, const uint4* __restrict__ base, size_t rec, size_t nrec, int lane)
-{
-    if constexpr (BK == 0) cp_async16(st + lane * 16, (const uint8_t*)(base + rec));
-    else
+    __device__ __forceinline__ void init(const void* plane, size_t nrec, size_t unit0, int lane)
     {
-        static_assert(ResidualSlots<BK>::end <= 512, "base record does not fit the base part of a stage");
-        copy_record<BK>(st, (const uint8_t*)base, rec, nrec, lane);
+        const uint8_t* p = (const uint8_t*)plane;
+        if constexpr (L::n128) { p128 = p + unit0 * 512 + lane * 16; p += nrec * 16; }
+        if constexpr (L::has64) { p64 = p + unit0 * 256 + lane * 8; p += nrec * 8; }
+        if constexpr (L::has32) { p32 = p + unit0 * 128 + lane * 4; p += nrec * 4; }
+        if constexpr (L::has16) { p16 = p + unit0 * 64 + (lane >> 1) * 4; p += nrec * 2; }
+        if constexpr (L::T != 0) ptail = p + unit0 * (4 * L::T) + ((lane * L::T) >> 5) * 4;
     }
-}
-template <int BK>
-__device__ __forceinline__ void read_base(uint32_t* wb, const uint8_t* st, size_t rec, int lane)
-{
-    if constexpr (BK == 0)
+    __device__ __forceinline__ void copy(uint8_t* st, int u, int lane) const
     {
-        const uint4 b = *(const uint4*)(st + lane * 16);
-        wb[0] = b.x; wb[1] = b.y; wb[2] = b.z; wb[3] = b.w;
+        if constexpr (L::n128) cp_async16(st + L::o128 + lane * 16, p128 + (size_t)u * 512);
+        if constexpr (L::has64) cp_async8(st + L::o64 + lane * 8, p64 + (size_t)u * 256);
+        if constexpr (L::has32) cp_async4(st + L::o32 + lane * 4, p32 + (size_t)u * 128);
+        if constexpr (L::has16) cp_async4(st + L::o16 + lane * 4, p16 + (size_t)u * 64);
+        if constexpr (L::T != 0)
+        {
+            const uint8_t* q = ptail + (size_t)u * (4 * L::T);
+            if constexpr (L::tail2) { cp_async4(st + L::otail + lane * 8, q); cp_async4(st + L::otail + lane * 8 + 4, q + 4); }
+            else cp_async4(st + L::otail + lane * 4, q);
+        }
     }
-    else read_record<BK>(wb, st, rec, lane);
-}
+    // the lane's record as stream words w[0 .. kWords), bits past the record zero
+    static __device__ __forceinline__ void read(uint32_t* w, const uint8_t* st, int lane)
+    {
+        int k = 0;
+        if constexpr (L::n128) { const uint4 v = *(const uint4*)(st + L::o128 + lane * 16); w[k++] = v.x; w[k++] = v.y; w[k++] = v.z; w[k++] = v.w; }
+        if constexpr (L::has64) { const uint2 v = *(const uint2*)(st + L::o64 + lane * 8); w[k++] = v.x; w[k++] = v.y; }
+        if constexpr (L::has32) w[k++] = *(const uint32_t*)(st + L::o32 + lane * 4);
+        if constexpr (L::has16) w[k++] = __byte_perm(*(const uint32_t*)(st + L::o16 + lane * 4), 0u, (lane & 1) ? 0x4432 : 0x4410);
+        if constexpr (L::T != 0)
+        {
+            const int sh = (lane * L::T) & 31;
+            uint32_t v;
+            if constexpr (L::tail2)
+            {
+                const uint2 t = *(const uint2*)(st + L::otail + lane * 8);
+                v = __funnelshift_r(t.x, t.y, sh);
+            }
+            else v = *(const uint32_t*)(st + L::otail + lane * 4) >> sh;
+            v &= (1u << L::T) - 1u;
+            if constexpr (L::tail_joins) w[k - 1] |= v << 16;
+            else w[k++] = v;
+        }
+    }
+};
 
 }  // namespace nq

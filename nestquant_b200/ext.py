@@ -58,7 +58,7 @@ def pf_pre(x, pt, pe, table, xg, xu, zg, I, kperm=False):
     R, H = pt.numel(), x.shape[1]
     if pe.numel() < R or xg.numel() < R * H or xu.numel() < R * H or zg.numel() < R * 4:
         raise NestQuantError("pf_pre sizes")
-    check(lib().nq_pf_pre(ptr(x), ptr(pt), ptr(pe), R, ptr(table), ptr(xg), ptr(xu), ptr(zg), H, I, int(bool(kperm)), current_stream()), "pf_pre")
+    check(lib().nq_pf_pre(ptr(x), ptr(pt), ptr(pe), R, ptr(table), table.shape[0], ptr(xg), ptr(xu), ptr(zg), H, I, int(bool(kperm)), current_stream()), "pf_pre")
 
 
 def pf_mid(acc_g, acc_u, zg, pe, table, h, zd, H, I, kperm=False):
@@ -68,7 +68,7 @@ def pf_mid(acc_g, acc_u, zg, pe, table, h, zd, H, I, kperm=False):
     R = pe.numel()
     if acc_g.numel() < R * I or acc_u.numel() < R * I or h.numel() < R * I or zd.numel() < R * 4 or zg.numel() < R * 4:
         raise NestQuantError("pf_mid sizes")
-    check(lib().nq_pf_mid(ptr(acc_g), ptr(acc_u), ptr(zg), ptr(pe), R, ptr(table), ptr(h), ptr(zd), H, I, int(bool(kperm)), current_stream()), "pf_mid")
+    check(lib().nq_pf_mid(ptr(acc_g), ptr(acc_u), ptr(zg), ptr(pe), R, ptr(table), table.shape[0], ptr(h), ptr(zd), H, I, int(bool(kperm)), current_stream()), "pf_mid")
 
 
 def pf_post(y, zd, pt, pe, prw, table, out, I):
@@ -78,19 +78,22 @@ def pf_post(y, zd, pt, pe, prw, table, out, I):
     R, H = pt.numel(), out.shape[1]
     if y.numel() < R * H or zd.numel() < R * 4 or prw.numel() < R or pe.numel() < R:
         raise NestQuantError("pf_post sizes")
-    check(lib().nq_pf_post(ptr(y), ptr(zd), ptr(pt), ptr(pe), ptr(prw), R, ptr(table), ptr(out), H, I, current_stream()), "pf_post")
+    check(lib().nq_pf_post(ptr(y), ptr(zd), ptr(pt), ptr(pe), ptr(prw), R, ptr(table), table.shape[0], ptr(out), H, I, current_stream()), "pf_post")
 
 
-def pf_combine(y, zd, pos, sel, rw, table, out, I):
-    """out[t] = sum_k rw[t,k] * (WHT128(y[pos[t,k]]) * sv_o + low rank) in pick order; out fp32 [T,H] is overwritten"""
+def pf_combine(y, zd, pos, sel, rw, table, out, I, pair0=0, npairs=None, accumulate=False):
+    """out[t] (+)= sum over the picks k of token t whose pair index pos[t,k] lies in [pair0, pair0 + npairs), in pick order, of
+    rw[t,k] * (WHT128(y[pos[t,k] - pair0]) * sv_o + low rank).  y fp32 [npairs,H] and zd [npairs,4] hold that window of the
+    expert-sorted pairs; npairs=None: the window is every pair.  accumulate=False overwrites out fp32 [T,H]."""
     _need(y, torch.float32, "y"); _need(zd, torch.float32, "zd"); _need(pos, torch.int32, "pos"); _need(sel, torch.int64, "sel")
     _need(rw, torch.float16, "rw"); _need(table, torch.int64, "table"); _need(out, torch.float32, "out")
     T, topk = sel.shape
     H = out.shape[1]
-    if pos.numel() < T * topk or rw.numel() < T * topk or out.numel() < T * H or y.numel() < T * topk * H or zd.numel() < T * topk * 4:
+    npairs = T * topk if npairs is None else npairs
+    if pos.numel() < T * topk or rw.numel() < T * topk or out.numel() < T * H or y.numel() < npairs * H or zd.numel() < npairs * 4:
         raise NestQuantError("pf_combine sizes")
     check(lib().nq_pf_combine(ptr(y), ptr(zd), ptr(pos), ptr(sel), ptr(rw), T, topk, ptr(table), table.shape[0], ptr(out), H, I,
-                              current_stream()), "pf_combine")
+                              pair0, npairs, int(bool(accumulate)), current_stream()), "pf_combine")
 
 
 def pf_plan_ints(E, pairs):
@@ -124,6 +127,23 @@ def pf_hits(counts, hits_ptr):
         return
     _need(counts, torch.int32, "counts")
     check(lib().nq_pf_hits(ptr(counts), hits_ptr, counts.numel(), current_stream()), "pf_hits")
+
+
+def operand_order(K):
+    """int64 [K]: position of element k of a row in the "operand order" of the decode path's internal fp16 rows (h and the
+    rotated inputs): inside every 128 consecutive k, k = 16 T + 2 t4 + 8 hi + e sits at 32 t4 + 4 T + 2 hi + e"""
+    k = torch.arange(K)
+    kk = k % 128
+    T, q = kk >> 4, kk & 15
+    return (k - kk) + 32 * ((q & 7) >> 1) + 4 * T + 2 * (q >> 3) + (q & 1)
+
+
+def kperm_order(K):
+    """int64 [K]: position of element k of a row in the k order the fused prefill GEMM reads (pf_pre / pf_mid with
+    kperm=True): inside every 16 consecutive k, position 4 i + {0, 1} holds k = 2 i + {0, 1} and 4 i + {2, 3} holds 8 + 2 i + {0, 1}"""
+    k = torch.arange(K)
+    q = k % 16
+    return (k - q) + 4 * ((q & 7) >> 1) + 2 * (q >> 3) + (q & 1)
 
 
 def default_ksplit(B, H, I, share=1.0):

@@ -8,11 +8,8 @@ error behaviour) so scripts written against it run unchanged:
 Everything that computes runs in the CUDA library behind nestquant_b200.ext; there is no torch or CPU fallback here
 (the dense reference decode of the original module lives in the test oracle, not in this package).
 """
-import math
-
 import torch
 
-from . import capi
 from . import ext as _ext
 
 TBL_W = 20
@@ -321,6 +318,10 @@ class MoELayer:
         return out
 
 
+    def status(s):
+        """0, or 1 if a device-side wait of a decode-path call ran out (its outputs are then invalid).  Synchronises."""
+        return int(s.cnt_h[0].item())
+
     def capture(s, B, with_mailbox=None, host_io=False):
         """Capture one B-token layer call in a CUDA graph over static buffers and return the handle:
         .x [B,H] fp16, .sel [B,topk] int64, .rw [B,topk] fp16, .out [B,H] fp32 (device), .replay().
@@ -369,97 +370,82 @@ class MoELayer:
             body()
         return g
 
-    def prefill(s, x, sel, rw, out=None, R=None, G=None, table=None, deterministic=True, fused=True):
-        """T > Bmax tokens: every routed expert decoded once (level read from the live table row), grouped GEMMs with fp32
-        outputs, same math as __call__.  x fp16 [T,H], sel int64 [T,topk], rw fp16 [T,topk] -> fp32 [T,H].
-        R: pairs per scratch chunk, G: experts decoded per group.  deterministic: sum each token's picks in pick order
-        (needs an fp32 [T*topk, H] buffer) instead of atomic adds.
-        fused=True: the trellis decode runs inside the grouped GEMM (tcgen05 / TMEM), dense weights never touch HBM and the
-        pass list is built on the device; the only host sync is the status read at the end.  fused=False: the reference's
-        structure (decode G experts to dense fp16, per-expert library GEMMs, one host sync for the counts)."""
+    def prefill(s, x, sel, rw, out=None, R=None, G=None, table=None):
+        """T > Bmax tokens: pairs (token, pick) sorted by expert, each routed expert decoded inside the grouped GEMM (tcgen05 /
+        TMEM; dense weights never touch HBM), same math as __call__.  x fp16 [T,H], sel int64 [T,topk], rw fp16 [T,topk] ->
+        fp32 [T,H].  Same call shape as the reference's prefill (sm120/moe.py:282-327).
+        R: pairs per scratch chunk (default 65536 = an 8192-token window of top-8 picks; the scratch, ~45 KB per pair at
+        the GLM shape, is allocated once per R and kept).  The expert-sorted pair list is processed chunk by chunk and each
+        token's picks are added chunk after chunk in pick order, so the result is bitwise repeatable for a given R.
+        G (experts decoded per group in the reference) is accepted and ignored: nothing is decoded ahead of the GEMM.
+        Picks whose expert id is outside [0, E) (e.g. -1 padding) are ignored, as on the decode path.
+        Nothing here synchronises with the host; a device-side time-out inside the GEMM raises a flag that
+        prefill_status() reads."""
         assert x.dtype == torch.float16 and rw.dtype == torch.float16 and sel.dtype == torch.int64, (x.dtype, rw.dtype, sel.dtype)
         T, k = sel.shape
         H, I, E, M, dev = s.H, s.I, s.E, s.M, x.device
         tb = s.table if table is None else table
-        R = R or 8192
-        G = G or 16
-        f16, f32, i32 = torch.float16, torch.float32, torch.int32
-        out = torch.empty(T, H, dtype=f32, device=dev) if out is None else out
-        flat, rwf = sel.reshape(-1), rw.reshape(-1)
-        order = torch.argsort(flat, stable=True)
-        pe, pt, prw = flat[order].to(i32), (order // k).to(i32), rwf[order].contiguous()
-        one = torch.ones_like(flat, dtype=i32)
-        cnt = torch.zeros(E, dtype=i32, device=dev).scatter_add_(0, flat, one)
-        if s.hits_ptr:
-            M.pf_hits(torch.zeros(E + 1, dtype=i32, device=dev).scatter_add_(0, torch.where(rwf != 0, flat, E), one)[:E].contiguous(), s.hits_ptr)
-        if fused:
-            P = T * k
-            pos = torch.empty(P, dtype=i32, device=dev)
-            pos[order] = torch.arange(P, dtype=i32, device=dev)
-            plan = torch.empty(M.pf_plan_ints(E, P), dtype=i32, device=dev)
-            M.pf_plan(cnt, tb, plan, P)
-            status = torch.zeros(1, dtype=i32, device=dev)
-            xg, xu = torch.empty(P, H, dtype=f16, device=dev), torch.empty(P, H, dtype=f16, device=dev)
-            zg, zd = torch.zeros(P, 4, dtype=f32, device=dev), torch.zeros(P, 4, dtype=f32, device=dev)
-            M.pf_pre(x, pt, pe, tb, xg, xu, zg, I, kperm=True)
-            acc_g, acc_u = torch.empty(P, I, dtype=f32, device=dev), torch.empty(P, I, dtype=f32, device=dev)
-            M.pf_gemm(tb, plan, xg, xu, acc_g, acc_u, H, I, s.nm_gu, s.nm_dn, False, status)
-            del xg, xu
-            hbuf = torch.empty(P, I, dtype=f16, device=dev)
-            M.pf_mid(acc_g, acc_u, zg, pe, tb, hbuf, zd, H, I, kperm=True)
-            del acc_g, acc_u
-            y = torch.empty(P, H, dtype=f32, device=dev)
-            M.pf_gemm(tb, plan, hbuf, None, y, None, H, I, s.nm_gu, s.nm_dn, True, status)
-            M.pf_combine(y, zd, pos, sel, rw, tb, out, I)
-            if int(status.item()):
-                raise capi.NestQuantError("prefill: a device-side wait timed out inside the grouped GEMM; results are invalid")
-            return out
-        cnt = cnt.cpu().tolist()
-        start, o = [0] * E, 0
-        for e in range(E):
-            start[e] = o; o += cnt[e]
-        live = [e for e in range(E) if cnt[e]]
         P = T * k
-        if deterministic:
-            y_all = torch.empty(P, H, dtype=f32, device=dev)
-            zd_all = torch.zeros(P, 4, dtype=f32, device=dev)
-            pos = torch.empty(P, dtype=i32, device=dev)
-            pos[order] = torch.arange(P, dtype=i32, device=dev)
-        else:
-            out.zero_()
-        Wgu = torch.empty(G, 2 * I, H, dtype=f16, device=dev)
-        Wdn = torch.empty(G, H, I, dtype=f16, device=dev)
-        xg, xu = torch.empty(R, H, dtype=f16, device=dev), torch.empty(R, H, dtype=f16, device=dev)
-        acc = torch.empty(2, R, I, dtype=f32, device=dev)
-        hbuf = torch.empty(R, I, dtype=f16, device=dev)
-        zg = torch.zeros(R, 4, dtype=f32, device=dev)
-        zd = torch.zeros(R, 4, dtype=f32, device=dev)
-        ybuf = None if deterministic else torch.empty(R, H, dtype=f32, device=dev)
-        ids = torch.tensor(live, dtype=i32, device=dev)
-        mm = torch.ops.aten.mm.dtype_out
-        for g0 in range(0, len(live), G):
-            grp = live[g0:g0 + G]
-            M.pf_decode(tb, ids[g0:g0 + len(grp)], Wgu, Wdn, H, I, s.nm_gu, s.nm_dn)
-            a, b = start[grp[0]], start[grp[-1]] + cnt[grp[-1]]
-            for c in range(a, b, R):
-                d = min(b, c + R); n = d - c
-                M.pf_pre(x, pt[c:d], pe[c:d], tb, xg, xu, zg, I)
-                y = y_all[c:d] if deterministic else ybuf[:n]
-                segs = []
-                for j, e in enumerate(grp):
-                    u, v = max(start[e], c) - c, min(start[e] + cnt[e], d) - c
-                    if v > u:
-                        segs.append((j, u, v))
-                for j, u, v in segs:
-                    mm(xg[u:v], Wgu[j, :I].t(), f32, out=acc[0, u:v]); mm(xu[u:v], Wgu[j, I:].t(), f32, out=acc[1, u:v])
-                M.pf_mid(acc[0], acc[1], zg, pe[c:d], tb, hbuf, zd_all[c:d] if deterministic else zd, H, I)
-                for j, u, v in segs:
-                    mm(hbuf[u:v], Wdn[j].t(), f32, out=y[u:v])
-                if not deterministic:
-                    M.pf_post(y, zd, pt[c:d], pe[c:d], prw[c:d], tb, out, I)
-        if deterministic:
-            M.pf_combine(y_all, zd_all, pos, sel, rw, tb, out, I)
+        R = max(1, min(R or 65536, P))
+        i32 = torch.int32
+        out = torch.empty(T, H, dtype=torch.float32, device=dev) if out is None else out
+        if P == 0:
+            return out
+        sc = s._prefill_scratch(R, dev)
+        flat, rwf = sel.reshape(-1), rw.reshape(-1)
+        # bin E collects the picks that contribute nothing: no valid expert id, expert not resident here, zero weight.  They
+        # sort behind every real pair and get no pass; the kernels skip their rows.
+        live = (flat >= 0) & (flat < E) & (rwf != 0)
+        live &= tb[flat.clamp(0, E - 1), 0] > 0
+        key = torch.where(live, flat, E)
+        order = torch.argsort(key, stable=True)
+        pe, pt = key[order].to(i32), (order // k).to(i32)
+        one = torch.ones_like(key, dtype=i32)
+        cnt = torch.zeros(E + 1, dtype=i32, device=dev).scatter_add_(0, key, one)
+        pos = torch.empty(P, dtype=i32, device=dev)
+        pos[order] = torch.arange(P, dtype=i32, device=dev)
+        if s.hits_ptr:
+            hit = torch.where((flat >= 0) & (flat < E) & (rwf != 0), flat, E)      # every pick with a weight, whatever the level
+            M.pf_hits(torch.zeros(E + 1, dtype=i32, device=dev).scatter_add_(0, hit, one)[:E].contiguous(), s.hits_ptr)
+        end = torch.cumsum(cnt, 0, dtype=i32)
+        start = end - cnt
+        for c0 in range(0, P, R):
+            n = min(R, P - c0)
+            # pairs of each expert inside this chunk -> pass list (built on the device, no host sync)
+            cnt_c = (torch.clamp(end, max=c0 + n) - torch.clamp(start, min=c0)).clamp_(min=0)[:E].contiguous()
+            M.pf_plan(cnt_c, tb, sc["plan"], n)
+            xg, xu, y = sc["xg"][:n], sc["xu"][:n], sc["y"][:n]
+            M.pf_pre(x, pt[c0:c0 + n], pe[c0:c0 + n], tb, xg, xu, sc["zg"], I, kperm=True)
+            M.pf_gemm(tb, sc["plan"], xg, xu, sc["acc_g"], sc["acc_u"], H, I, s.nm_gu, s.nm_dn, False, sc["status"])
+            M.pf_mid(sc["acc_g"], sc["acc_u"], sc["zg"], pe[c0:c0 + n], tb, sc["h"], sc["zd"], H, I, kperm=True)
+            M.pf_gemm(tb, sc["plan"], sc["h"][:n], None, y, None, H, I, s.nm_gu, s.nm_dn, True, sc["status"])     # y overwrites xg | xu
+            M.pf_combine(y, sc["zd"], pos, sel, rw, tb, out, I, pair0=c0, npairs=n, accumulate=c0 > 0)
         return out
+
+    def _prefill_scratch(s, R, dev):
+        """scratch of the prefill path for chunks of R pairs, kept between calls (the reference's pf_scratch,
+        sm120/moe.py:263-275, without its dense weight buffers): xg | xu fp16 [R,H] each, aliased by y fp32 [R,H];
+        acc_g, acc_u fp32 [R,I]; h fp16 [R,I]; zg, zd fp32 [R,4]; the pass list; the status word"""
+        sc = getattr(s, "_pf_sc", None)
+        if sc is not None and sc["R"] == R and sc["y"].device == dev:
+            return sc
+        H, I, E = s.H, s.I, s.E
+        f16, f32, i32 = torch.float16, torch.float32, torch.int32
+        y = torch.empty(R, H, dtype=f32, device=dev)
+        halves = y.view(-1).view(f16)
+        status = sc["status"] if sc is not None and sc["status"].device == dev else torch.zeros(1, dtype=i32, device=dev)
+        s._pf_sc = dict(R=R, y=y, xg=halves[:R * H].view(R, H), xu=halves[R * H:].view(R, H),
+                        acc_g=torch.empty(R, I, dtype=f32, device=dev), acc_u=torch.empty(R, I, dtype=f32, device=dev),
+                        h=torch.empty(R, I, dtype=f16, device=dev), zg=torch.zeros(R, 4, dtype=f32, device=dev),
+                        zd=torch.zeros(R, 4, dtype=f32, device=dev),
+                        plan=torch.empty(s.M.pf_plan_ints(E, R), dtype=i32, device=dev), status=status)
+        return s._pf_sc
+
+    def prefill_status(s):
+        """0, or 1 if a device-side wait inside the prefill GEMM has run out since the layer was built (results of that call are
+        invalid).  Synchronises with the device."""
+        sc = getattr(s, "_pf_sc", None)
+        return 0 if sc is None else int(sc["status"].item())
 
 
 class _Captured:

@@ -30,7 +30,7 @@ def test_format_queries_need_no_gpu():
         assert lib.nq_plane_bytes(12288 * 32, c) == moe.proj_sizes(4096, 6144, None, c)["p4"]
     assert lib.nq_plane_bytes(32, 10) == 0
     w = ext.moe_workspace(4, 8, 6144, 2048, 2, 1)
-    assert w["acc_gu_floats"] == 2 * 32 * 4096 and w["acc_d_floats"] == 32 * 6144 and w["wq_ints"] == 4 and w["cnt_gu_ints"] == 2 * 32 * 16
+    assert w["acc_gu_floats"] == 2 * 32 * 4096 and w["acc_d_floats"] == 32 * 6144 and w["wq_ints"] == 4 and w["cnt_gu_ints"] == 2 * 32 * 16 + 32
     from nestquant_b200.capi import NestQuantError
     with pytest.raises(NestQuantError):
         ext.moe_workspace(33, 8, 6144, 2048, 1, 1)

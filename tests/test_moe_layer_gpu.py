@@ -134,7 +134,8 @@ def test_pattern_rate_base_layer_decode_and_prefill():
     x = torch.randn(T, H, generator=gen).bfloat16().half()
     ref = O.moe_ref(exs_o, levels, x.numpy(), sel.numpy(), rw.numpy())
     y = L.prefill(x.cuda(), sel.cuda(), rw.cuda())
-    y_lib = L.prefill(x.cuda(), sel.cuda(), rw.cuda(), fused=False)
+    from tests.prefill_lib import prefill_library
+    y_lib = prefill_library(L, x.cuda(), sel.cuda(), rw.cuda())
     torch.cuda.synchronize()
     for got in (y, y_lib):
         ma, rl = layer_errors(got.cpu().numpy(), ref)

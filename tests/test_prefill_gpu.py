@@ -9,6 +9,7 @@ import torch
 
 from oracle import nq_oracle as O
 from tests.golden_io import layer_from
+from tests.prefill_lib import prefill_library
 from tests.util import MAX_ABS_TOL, REL_L2_TOL, expert_to_device, expert_to_oracle, layer_errors
 
 pytestmark = pytest.mark.gpu
@@ -30,19 +31,21 @@ def _layer_from_golden(name, **kw):
 @pytest.mark.parametrize("deterministic,fused", [(True, True), (True, False), (False, False)])
 def test_golden_layer_prefill(deterministic, fused):
     g, L, keep, x, sel, rw = _layer_from_golden("layer.npz", nm_gu=1, nm_dn=1)
-    y = L.prefill(x, sel, rw, deterministic=deterministic, fused=fused)
+    y = L.prefill(x, sel, rw) if fused else prefill_library(L, x, sel, rw, deterministic=deterministic)
     torch.cuda.synchronize()
     ma, rl = layer_errors(y.cpu().numpy(), g["out"])
     assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL and rl <= 5e-4, (ma, rl)
     assert not y[4].any()
     if deterministic:
-        assert torch.equal(y, L.prefill(x, sel, rw, fused=fused))
+        assert torch.equal(y, L.prefill(x, sel, rw) if fused else prefill_library(L, x, sel, rw))
+    assert L.prefill_status() == 0
 
 
 def test_golden_layer_with_low_rank_and_wide_rotation():
     g, L, keep, x, sel, rw = _layer_from_golden("layer_lr.npz")
     for fused in (True, False):
-        y = L.prefill(x, sel, rw, R=4, G=1, fused=fused)           # tiny chunks: exercises the group / chunk loops
+        # tiny chunks: exercises the chunk loops (fused: chunks of 5 pairs cut experts' pair ranges in two)
+        y = L.prefill(x, sel, rw, R=5) if fused else prefill_library(L, x, sel, rw, R=4, G=1)
         torch.cuda.synchronize()
         ma, rl = layer_errors(y.cpu().numpy(), g["out"])
         assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL and rl <= 5e-4, (fused, ma, rl)
@@ -77,7 +80,7 @@ def test_prefill_matches_decode_path_and_oracle():
     rw = torch.softmax(tv, 1).half()
     rw[7, 1] = 0
     xd, seld, rwd = x.cuda(), sel.cuda(), rw.cuda()
-    y_lib = L.prefill(xd, seld, rwd, R=64, G=3, fused=False)
+    y_lib = prefill_library(L, xd, seld, rwd, R=64, G=3)
     hits.zero_()
     y = L.prefill(xd, seld, rwd)
     torch.cuda.synchronize()
@@ -105,7 +108,7 @@ def test_prefill_glm_shape_fused_matches_library_gemm():
     sel, rw = synth.routing(T, cfg["E"], cfg["topk"], 12)
     x = synth.tokens(T, cfg["H"], 13).cuda()
     sel, rw = sel.cuda(), rw.cuda()
-    y_lib = L.prefill(x, sel, rw, fused=False)
+    y_lib = prefill_library(L, x, sel, rw)
     y = L.prefill(x, sel, rw)
     y2 = L.prefill(x, sel, rw)
     yh = L.prefill(x, sel, (rw.float() * 0.5).half())
@@ -134,7 +137,7 @@ def test_prefill_many_tokens_per_expert():
     counts = torch.bincount(sel.reshape(-1), minlength=NE).tolist()
     assert max(counts) > 768 and any(256 < c <= 384 for c in counts), counts      # 3 passes for one expert, a split tile for another
     xd, seld, rwd = x.cuda(), sel.cuda(), rw.cuda()
-    y_lib = L.prefill(xd, seld, rwd, fused=False)
+    y_lib = prefill_library(L, xd, seld, rwd)
     y = L.prefill(xd, seld, rwd)
     torch.cuda.synchronize()
     assert layer_errors(y.cpu().numpy(), y_lib.cpu().numpy())[1] <= 1e-4
