@@ -16,11 +16,11 @@
 //             view starts on a word); a view serves up to three windows, at its byte offsets 0, 1 and 2, each by one
 //             instruction (and / byte-permute / shift).
 //   hash      one 32-bit multiply per window.
-//   byte sums SUM_MMA: one mma.m16n8k32.u8 adds the bytes of four hashed words per lane at once: the hashed words are
-//             the A fragment, the B fragment is a per-lane selector (each lane's own k-group routed to its own two
-//             accumulator columns) whose non-zero bytes are 1 (level 2) or Mb, N (level 4, second MMA chained through the
-//             accumulator), and the accumulator starts at the bit pattern that turns the sum into fp16(1024 + S).
-//             SUM_DP4A: the same sums by one dp4a per hashed word (two at level 4).
+//   byte sums one dp4a per hashed word (two at level 4, with Mb and N as the byte weights), accumulating onto the bit pattern
+//             that turns the sum into fp16(1024 + S).  (The same sums on the tensor pipe - one mma.m16n8k32.u8 per four
+//             hashed words, a per-lane selector as the B fragment - were built and measured: legacy mma.sync issues at
+//             0.5 per clock per SM on this part, exactly the pipe time of the four dp4a it replaces, and the kernels ran
+//             no faster, so that variant is not kept.)
 //   affine    one byte-permute packs two sums, one fp16x2 fma applies the unit's multiplier and addend (single rounding).
 #pragma once
 #include <cuda_fp16.h>
@@ -34,12 +34,6 @@ constexpr uint32_t kMul1A2 = 0x1eee1eeeu;   // fp16x2 A
 constexpr uint32_t kMul1B2 = 0xc931c931u;   // fp16x2 B
 constexpr int kTableWidth = 20;              // int64 words per expert row of the device table
 constexpr int kNumCodes = 10;
-
-enum { SUM_DP4A = 0, SUM_MMA = 1 };
-#ifndef NQ_SUM
-#define NQ_SUM 1
-#endif
-constexpr int kSumDefault = NQ_SUM;
 
 // ---------------------------------------------------------------- window patterns (the format's tables)
 __host__ __device__ constexpr int pattern_ka(int code)
@@ -140,40 +134,12 @@ __device__ __forceinline__ uint32_t fma_h2(uint32_t a, uint32_t b, uint32_t c)
     asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-// d[i] = c[i] + sum over the lane's own hashed bytes selected by (b0, b1): see ByteSelect
-__device__ __forceinline__ void mma_bytes(uint32_t (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
-                                          uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3)
-{
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
-}
-// Selector fragment of the byte-sum MMA.  In m16n8k32 lane (g, t4) owns A columns k = 4 t4 .. 4 t4 + 3 (registers 0, 1:
-// rows g, g + 8) and k = 16 + 4 t4 .. (registers 2, 3), and accumulator columns 2 t4, 2 t4 + 1.  B[k][n] is non-zero
-// only for (k in 4 t4 .. 4 t4 + 3, n = 2 t4) and (k in 16 + 4 t4 .., n = 2 t4 + 1), so d0, d1 = byte sums of A registers
-// 0, 2 (row g) and d2, d3 = of registers 1, 3 (row g + 8): every lane gets the sums of its own four words back.
-// The B fragment of lane (g, t4) holds column n = g: its first register (k = 4 t4 ..) is live iff g == 2 t4, its
-// second (k = 16 + 4 t4 ..) iff g == 2 t4 + 1.
-struct ByteSelect
-{
-    uint32_t even, odd;     // all-ones byte masks
-};
-__device__ __forceinline__ ByteSelect byte_select(int lane)
-{
-    const int g = lane >> 2, t4 = lane & 3;
-    ByteSelect s;
-    s.even = g == 2 * t4 ? 0xFFFFFFFFu : 0u;
-    s.odd = g == 2 * t4 + 1 ? 0xFFFFFFFFu : 0u;
-    return s;
-}
-
 // Per-unit multipliers.  a2 / c2: fp16x2 multiplier and addend with the ring sign folded in (negating both negates the
-// result exactly).  level 2: weights of both byte sums are 1.  level 4: Mb for the base sum, N for the residual sum.
-// SUM_MMA keeps them as selector fragments (m0, m1 / n0, n1), SUM_DP4A as replicated bytes in m0 / n0.
+// result exactly).  m / n: byte weights of the base and the residual sum, replicated into four bytes (1 and 0 at level 2,
+// Mb and N at level 4).
 struct UnitConsts
 {
-    uint32_t a2, c2;
-    uint32_t m0, m1, n0, n1;
+    uint32_t a2, c2, m, n;
 };
 // Block word Mb | N << 8 -> fp16 multiplier A' (low half) and addend C' (high half), each fp32 operation rounded on its
 // own in the order the format defines (sm120/ref15_spec.py:79-83, sm120/moe.py:130-132):
@@ -186,25 +152,18 @@ __device__ __forceinline__ uint32_t block_multipliers(uint32_t block_word)
     const float c = __fsub_rn(__fadd_rn(__fmul_rn(ratio, -3.453125f), -3.453125f), __fmul_rn(1024.0f, __half2float(a)));
     return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(__float2half_rn(c)) << 16);
 }
-template <int SUM>
-__device__ __forceinline__ UnitConsts consts_level2(uint32_t sign2, const ByteSelect& sel)
+__device__ __forceinline__ UnitConsts consts_level2(uint32_t sign2)
 {
     UnitConsts k;
-    k.a2 = kMul1A2 ^ sign2; k.c2 = kMul1B2 ^ sign2;
-    if constexpr (SUM == SUM_MMA) { k.m0 = sel.even & 0x01010101u; k.m1 = sel.odd & 0x01010101u; }
-    else { k.m0 = 0x01010101u; k.m1 = 0u; }
-    k.n0 = k.n1 = 0u;
+    k.a2 = kMul1A2 ^ sign2; k.c2 = kMul1B2 ^ sign2; k.m = 0x01010101u; k.n = 0u;
     return k;
 }
 // ac = block_multipliers(word), mbn = the block word
-template <int SUM>
-__device__ __forceinline__ UnitConsts consts_level4(uint32_t ac, uint32_t mbn, uint32_t sign2, const ByteSelect& sel)
+__device__ __forceinline__ UnitConsts consts_level4(uint32_t ac, uint32_t mbn, uint32_t sign2)
 {
     UnitConsts k;
     k.a2 = __byte_perm(ac, 0u, 0x1010) ^ sign2; k.c2 = __byte_perm(ac, 0u, 0x3232) ^ sign2;
-    const uint32_t m = __byte_perm(mbn, 0u, 0x0000), n = __byte_perm(mbn, 0u, 0x1111);
-    if constexpr (SUM == SUM_MMA) { k.m0 = m & sel.even; k.m1 = m & sel.odd; k.n0 = n & sel.even; k.n1 = n & sel.odd; }
-    else { k.m0 = m; k.n0 = n; k.m1 = k.n1 = 0u; }
+    k.m = __byte_perm(mbn, 0u, 0x0000); k.n = __byte_perm(mbn, 0u, 0x1111);
     return k;
 }
 
@@ -212,60 +171,31 @@ __device__ __forceinline__ UnitConsts consts_level4(uint32_t ac, uint32_t mbn, u
 // a[q] = fp16x2 of lane weights 2 (4 T + q) and 2 (4 T + q) + 1.
 // RES: refined (level 4) unit, RC its residual window code, BK the window code of the base stream (0 = 2 bits per weight
 // in 128-bit records; 1 = 1.75 bits per weight in 112-bit records, sm120/NQ_RES_V2.md:36-50: only the base state walk
-// changes).  All 32 lanes must call it together when SUM == SUM_MMA.
-template <bool RES, int RC, int BK, int T, int SUM>
+// changes).
+template <bool RES, int RC, int BK, int T>
 __device__ __forceinline__ void decode_kstep(const uint32_t* wb, const uint32_t* wr, const UnitConsts& k, uint32_t (&a)[4])
 {
+    using std::integral_constant;
     // hashed base / residual word of lane weight 8 T + i
     auto hb = [&](auto ic) { return state16<BK, 8 * T + decltype(ic)::value>(wb) * kHashMul; };
     auto hr = [&](auto ic) { return state16<RC, 8 * T + decltype(ic)::value>(wr) * kHashMul; };
-    using std::integral_constant;
-    if constexpr (SUM == SUM_MMA)
-    {
-        // one MMA per two fragment registers: A = {w(q, 0), w(q + 1, 0), w(q, 1), w(q + 1, 1)} -> d0, d1 = sums of
-        // pair q, d2, d3 = sums of pair q + 1
-        static_for<2>([&](auto hc) {
-            constexpr int q = 2 * decltype(hc)::value;
-            uint32_t d[4];
-            const uint32_t b0 = hb(integral_constant<int, 2 * q>{}), b1 = hb(integral_constant<int, 2 * q + 2>{});
-            const uint32_t b2 = hb(integral_constant<int, 2 * q + 1>{}), b3 = hb(integral_constant<int, 2 * q + 3>{});
-            if constexpr (!RES)
-            {
-                // 0x6400 + S is the fp16 bit pattern of 1024 + S (S <= 1020)
-                mma_bytes(d, b0, b1, b2, b3, k.m0, k.m1, 0x6400u, 0x6400u, 0x6400u, 0x6400u);
-                a[q] = fma_h2(__byte_perm(d[0], d[1], 0x5410), k.a2, k.c2);
-                a[q + 1] = fma_h2(__byte_perm(d[2], d[3], 0x5410), k.a2, k.c2);
-            }
-            else
-            {
-                // Mb Sb + N Sr + 128 + (0x6400 << 8): bits 8..23 are the fp16 pattern of 1024 + F
-                mma_bytes(d, b0, b1, b2, b3, k.m0, k.m1, 0x640080u, 0x640080u, 0x640080u, 0x640080u);
-                const uint32_t r0 = hr(integral_constant<int, 2 * q>{}), r1 = hr(integral_constant<int, 2 * q + 2>{});
-                const uint32_t r2 = hr(integral_constant<int, 2 * q + 1>{}), r3 = hr(integral_constant<int, 2 * q + 3>{});
-                mma_bytes(d, r0, r1, r2, r3, k.n0, k.n1, d[0], d[1], d[2], d[3]);
-                a[q] = fma_h2(__byte_perm(d[0], d[1], 0x6521), k.a2, k.c2);
-                a[q + 1] = fma_h2(__byte_perm(d[2], d[3], 0x6521), k.a2, k.c2);
-            }
-        });
-    }
-    else
-    {
-        static_for<4>([&](auto qc) {
-            constexpr int q = decltype(qc)::value;
-            if constexpr (!RES)
-            {
-                const uint32_t s0 = dot4(hb(integral_constant<int, 2 * q>{}), k.m0, 0x6400u);
-                const uint32_t s1 = dot4(hb(integral_constant<int, 2 * q + 1>{}), k.m0, 0x6400u);
-                a[q] = fma_h2(__byte_perm(s0, s1, 0x5410), k.a2, k.c2);
-            }
-            else
-            {
-                const uint32_t s0 = dot4(hr(integral_constant<int, 2 * q>{}), k.n0, dot4(hb(integral_constant<int, 2 * q>{}), k.m0, 0x640080u));
-                const uint32_t s1 = dot4(hr(integral_constant<int, 2 * q + 1>{}), k.n0, dot4(hb(integral_constant<int, 2 * q + 1>{}), k.m0, 0x640080u));
-                a[q] = fma_h2(__byte_perm(s0, s1, 0x6521), k.a2, k.c2);
-            }
-        });
-    }
+    static_for<4>([&](auto qc) {
+        constexpr int q = decltype(qc)::value;
+        if constexpr (!RES)
+        {
+            // 0x6400 + S is the fp16 bit pattern of 1024 + S (S <= 1020)
+            const uint32_t s0 = dot4(hb(integral_constant<int, 2 * q>{}), k.m, 0x6400u);
+            const uint32_t s1 = dot4(hb(integral_constant<int, 2 * q + 1>{}), k.m, 0x6400u);
+            a[q] = fma_h2(__byte_perm(s0, s1, 0x5410), k.a2, k.c2);
+        }
+        else
+        {
+            // Mb Sb + N Sr + 128 + (0x6400 << 8): bits 8..23 are the fp16 pattern of 1024 + F
+            const uint32_t s0 = dot4(hr(integral_constant<int, 2 * q>{}), k.n, dot4(hb(integral_constant<int, 2 * q>{}), k.m, 0x640080u));
+            const uint32_t s1 = dot4(hr(integral_constant<int, 2 * q + 1>{}), k.n, dot4(hb(integral_constant<int, 2 * q + 1>{}), k.m, 0x640080u));
+            a[q] = fma_h2(__byte_perm(s0, s1, 0x6521), k.a2, k.c2);
+        }
+    });
 }
 
 // ---------------------------------------------------------------- plane pointers of one projection of one expert

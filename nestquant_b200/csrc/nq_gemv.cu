@@ -38,7 +38,7 @@ namespace nq {
 #define NQ_GEMV_CODES 0x3FF
 #endif
 #ifndef NQ_GEMV_DEPTH
-#define NQ_GEMV_DEPTH 4          // stages of the plane ring per warp
+#define NQ_GEMV_DEPTH 3          // stages of the plane ring per warp
 #endif
 #ifndef NQ_GEMV_WARPS
 #define NQ_GEMV_WARPS 10         // warps per CTA (independent of one another; the first 8 also build the run list)
@@ -46,13 +46,9 @@ namespace nq {
 #ifndef NQ_GEMV_MINBLOCKS
 #define NQ_GEMV_MINBLOCKS 2      // resident CTAs per SM the kernel is compiled for: 20 warps per SM at <= 96 registers
 #endif
-#ifndef NQ_GEMV_SUM
-#define NQ_GEMV_SUM NQ_SUM
-#endif
 constexpr int kDepth = NQ_GEMV_DEPTH;
 constexpr int kWarps = NQ_GEMV_WARPS, kThreads = 32 * kWarps;
 static_assert(kThreads >= NQ_MAX_PICKS, "the run list is built by one thread per pick");
-constexpr int kGemvSum = NQ_GEMV_SUM;
 constexpr int kRunTiles = 4;     // column tiles (8 tokens each) of mma.m16n8k16 per run
 constexpr int kRunTokens = 8 * kRunTiles;
 constexpr int kRotBlocks = 4;    // 128-blocks per rotation piece
@@ -122,7 +118,7 @@ __device__ __forceinline__ bool wait_counter(const int* p, int target, int* stat
             if (t0 == 0) t0 = t;
             else if (t - t0 > kWaitNs) break;
         }
-        __nanosleep(40);
+        __nanosleep(100);
     }
     atomicExch(status, 1);
     return false;
@@ -201,98 +197,185 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// tokens of the run as the N operand: lane (g, t4) supplies k = 16 T + 2 t4 (+8) of token 8 nt + g.
-// xp[nt]: that token's row (operand order) + 64 t4 bytes, or null when the tile has no such token.
+// Tokens of the run as the N operand: lane (g, t4) supplies k = 16 T + 2 t4 (+8) of token 8 nt + g, i.e. column g of the
+// tile.  A tile column without a token reads the run's first token instead: MMA columns are independent, so whatever is
+// multiplied there lands in accumulators that are never stored.
+//
+// One column tile (runs of up to 8 tokens, the 1..8-token decode case): the 8 k-steps' (b0, b1) pairs of a unit are 64
+// contiguous bytes per lane, copied into the plane ring by cp.async together with the unit's records (lanes whose column
+// has a token only), so they are in shared memory when the unit is decoded.  A lane's four 16-byte pieces go to four
+// lane-indexed arrays (piece i of lane l at 512 i + 16 l): conflict-free, and addressed from the same per-lane register
+// as the base records.
+constexpr int kStageTokens = kStageBytes;            // offset of the token fragments inside a GEMV stage
+constexpr int kGemvStage = kStageBytes + 4 * 512;    // bytes per GEMV stage
+struct TokenSink1
+{
+    float (&acc)[4];
+    uint32_t frag;     // shared-space address of this stage's token fragments + 16 lane
+    template <int T>
+    __device__ __forceinline__ void operator()(std::integral_constant<int, T>, const uint32_t (&a)[4]) const
+    {
+        const uint2 b = lds64(frag + 512 * (T >> 1) + 8 * (T & 1));
+        mma_16816(acc, a, b.x, b.y);
+    }
+};
+// Up to NT column tiles: B fragments fetched from global memory per k-step.
 template <int NT>
-struct TokenSink
+struct TokenSinkN
 {
     float (&acc)[NT][4];
-    const uint8_t* const (&xp)[NT];
-    int ntiles, off;     // off = 256 * chunk
+    const uint8_t* x0;           // token rows (bytes)
+    const uint32_t (&xoff)[NT];  // byte offset of the tile's row for this lane (+ 64 t4)
+    int ntiles, off;             // off = 256 * chunk
     template <int T>
     __device__ __forceinline__ void operator()(std::integral_constant<int, T>, const uint32_t (&a)[4]) const
     {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
         {
-            if (NT > 1 && nt >= ntiles) break;      // warp-uniform
-            uint2 b = make_uint2(0u, 0u);
-            if (xp[nt]) b = *(const uint2*)(xp[nt] + off + T * 8);
+            if (nt >= ntiles) break;      // warp-uniform
+            const uint2 b = *(const uint2*)(x0 + xoff[nt] + off + T * 8);
             mma_16816(acc[nt], a, b.x, b.y);
         }
     }
 };
 
-// One warp, one strip, chunks [c0, c1): stream, decode, multiply.  REFINED: the expert is at level 4.  ring: this warp's
-// kDepth stages.  gate() runs once, after the first copies are on their way and before anything is multiplied.
-template <bool REFINED, int RC, int BK, int NT, class Gate>
-__device__ __forceinline__ void strip_gemv(const ProjPlanes& P, const StripRef& sr, int C, int NS, int c0, int c1, int lane,
-                                           float (&acc)[NT][4], const uint8_t* const (&xp)[NT], int ntiles, uint8_t* ring, Gate&& gate)
+// What one warp does with one strip: filled in by the caller, read once by strip_gemv.
+struct StripJob
 {
-    const ByteSelect sel = byte_select(lane);
-    const uint8_t* varp = P.var ? P.var + sr.unit0 : nullptr;     // ring-sign bytes / block words of this strip's units
-    const uint32_t* d4p = P.d4 + sr.res0;
+    ProjPlanes P;
+    StripRef sr;
+    int C, NS, c0, c1;               // chunks per strip, strips of the projection, chunk range [c0, c1)
+    const uint8_t* x0;               // token rows (operand order), as bytes
+    uint32_t xoff[kRunTiles];        // per column tile: byte offset of this lane's token row + 64 t4
+    int ntiles;
+    bool has_token;                  // this lane's column of tile 0 holds a token
+    uint32_t ring;                   // shared-space address of the warp's kDepth stages
+    const int* gate; int gate_target; int* status;   // counter to wait for before the first multiply (or null)
+};
+
+// One warp, one strip, chunks [c0, c1): stream, decode, multiply; acc = the 16 x (8 NT) partial sums.  REFINED: the expert
+// is at level 4.  false = the wait on the gate counter ran out.
+// Not inlined on purpose: each of the decoder variants gets a register allocation of its own, and the bookkeeping of the
+// piece loop is saved once per piece around the call instead of being squeezed into the decode loop.
+template <bool REFINED, int RC, int BK, int NT>
+__device__ __noinline__ bool strip_gemv(const StripJob& J, float (&out)[NT][4])
+{
+    const int lane = threadIdx.x & 31, c0 = J.c0, c1 = J.c1;
+    const unsigned long long flags = J.sr.flags;
     RecordCursor<BK> cb;
-    cb.init(P.base, (size_t)NS * C * 32, sr.unit0 + c0, lane);
+    cb.init(J.P.base, (size_t)J.NS * J.C * 32, J.sr.unit0 + c0, lane);
     RecordCursor<RC> cr;
     int issued = 0;                       // refined units whose copies are issued
-    if constexpr (REFINED) cr.init(P.p4, sr.res_nrec, sr.res0 + refined_before(sr, c0), lane);
-    auto issue = [&](int ch, uint8_t* st) {
+    if constexpr (REFINED) cr.init(J.P.p4, J.sr.res_nrec, J.sr.res0 + refined_before(J.sr, c0), lane);
+    const uint32_t ring = J.ring;
+    const uint8_t* xin = J.x0 + J.xoff[0] + (size_t)c0 * 256;       // next token fragment to copy (one column tile)
+    const bool has_token = J.has_token;
+    auto issue_planes = [&](int ch, uint32_t st) {
         cb.copy(st, ch - c0, lane);
         if constexpr (REFINED)
-            if (chunk_refined(sr, ch)) cr.copy(st + kStageBase, issued++, lane);
+            if ((flags >> ch) & 1ull) cr.copy(st + kStageBase, issued++, lane);
+    };      // (prologue only; the loop below tests its flags from a block-local copy)
+    auto issue_tokens = [&](uint32_t st) {
+        if constexpr (NT == 1)
+        {
+            if (has_token)
+            {
+                const uint32_t dst = st + kStageTokens + lane * 16;
+                cp_async16_at<0, 0>(dst, xin); cp_async16_at<512, 16>(dst, xin);
+                cp_async16_at<1024, 32>(dst, xin); cp_async16_at<1536, 48>(dst, xin);
+            }
+            xin += 256;
+        }
     };
+    // the planes can be fetched before the inputs exist (gate), the token fragments only after
+#pragma unroll
+    for (int d = 0; d < kDepth - 1; ++d)
+        if (c0 + d < c1) issue_planes(c0 + d, ring + d * kGemvStage);
+    bool ok = true;
+    if (J.gate) ok = wait_counter(J.gate, J.gate_target, J.status);
 #pragma unroll
     for (int d = 0; d < kDepth - 1; ++d)
     {
-        if (c0 + d < c1) issue(c0 + d, ring + d * kStageBytes);
+        if (c0 + d < c1) issue_tokens(ring + d * kGemvStage);
         cp_async_commit();
     }
-    gate();
-    int slot = 0, slot_in = kDepth - 1;
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+    uint32_t st = ring;                                   // stage to consume; the stage before it (cyclically) is filled
+    const int nxt = ring_successor(lane);
     for (int cs = c0; cs < c1; cs += 32)
     {
-        // per-unit scalars of chunks cs .. cs + 31, one chunk per lane: ring signs, block word and its multipliers
+        // per-unit scalars of chunks cs .. cs + 31, one chunk per lane: ring signs, block word and its multipliers;
+        // fl: refinement flags of chunks cs .. cs + 31 (+ kDepth - 1 for the copies that run ahead)
+        const unsigned long long fl = flags >> cs;
         uint32_t var_b = 0, ac = 0, mbn = 0;
         {
-            const int ch = cs + lane;
-            if (ch < c1)
+            const int cl = cs + lane;
+            if (cl < c1)
             {
-                if (varp) var_b = __ldg(varp + ch);
+                if (J.P.var) var_b = __ldg(J.P.var + J.sr.unit0 + cl);
                 if constexpr (REFINED)
-                    if (chunk_refined(sr, ch))
+                    if ((fl >> lane) & 1ull)
                     {
-                        mbn = __ldg(d4p + refined_before(sr, ch)) & 0xFFFFu;
+                        mbn = __ldg(J.P.d4 + J.sr.res0 + refined_before(J.sr, cl)) & 0xFFFFu;
                         ac = block_multipliers(mbn);
                     }
             }
         }
-        const int ce = cs + 32 < c1 ? cs + 32 : c1;
-        for (int ch = cs; ch < ce; ++ch)
+        const int n = c1 - cs < 32 ? c1 - cs : 32;
+        for (int i = 0; i < n; ++i)
         {
-            if (ch + kDepth - 1 < c1) issue(ch + kDepth - 1, ring + slot_in * kStageBytes);
+            const int ch = cs + i;
+            if (ch + kDepth - 1 < c1)
+            {
+                const uint32_t st_in = st == ring ? ring + (kDepth - 1) * kGemvStage : st - kGemvStage;
+                cb.copy(st_in, ch + kDepth - 1 - c0, lane);
+                if constexpr (REFINED)
+                    if ((fl >> (i + kDepth - 1)) & 1ull) cr.copy(st_in + kStageBase, issued++, lane);
+                issue_tokens(st_in);
+            }
             cp_async_commit();
             cp_async_wait<kDepth - 1>();
-            const uint8_t* st = ring + slot * kStageBytes;
-            slot = slot + 1 == kDepth ? 0 : slot + 1;
-            slot_in = slot_in + 1 == kDepth ? 0 : slot_in + 1;
-            const uint32_t sign2 = sign_mask(__shfl_sync(0xffffffffu, var_b, ch - cs), lane);
+            const uint32_t sign2 = sign_mask(__shfl_sync(0xffffffffu, var_b, i), lane);
             uint32_t wb[Pattern<BK>::kWords + 2], wr[Pattern<RC>::kWords + 2];
             RecordCursor<BK>::read(wb, st, lane);
-            const TokenSink<NT> sink{acc, xp, ntiles, ch * 256};
+            continue_stream<Pattern<BK>::kBits>(wb, __shfl_sync(0xffffffffu, wb[0], nxt));
             bool refined = false;
-            if constexpr (REFINED) refined = chunk_refined(sr, ch);
+            if constexpr (REFINED) refined = (fl >> i) & 1ull;
+            UnitConsts k;
             if (refined)
             {
-                const uint32_t acw = __shfl_sync(0xffffffffu, ac, ch - cs), mb = __shfl_sync(0xffffffffu, mbn, ch - cs);
+                const uint32_t acw = __shfl_sync(0xffffffffu, ac, i), mb = __shfl_sync(0xffffffffu, mbn, i);
                 RecordCursor<RC>::read(wr, st + kStageBase, lane);
-                decode_unit<true, RC, BK, kGemvSum>(wb, wr, consts_level4<kGemvSum>(acw, mb, sign2, sel), lane, sink);
+                continue_stream<Pattern<RC>::kBits>(wr, __shfl_sync(0xffffffffu, wr[0], nxt));
+                k = consts_level4(acw, mb, sign2);
+            }
+            else k = consts_level2(sign2);
+            if constexpr (NT == 1)
+            {
+                const TokenSink1 sink{acc[0], st + kStageTokens + lane * 16};
+                if (refined) decode_words<true, RC, BK>(wb, wr, k, sink);
+                else decode_words<false, 0, BK>(wb, wr, k, sink);
             }
             else
-                decode_unit<false, 0, BK, kGemvSum>(wb, wr, consts_level2<kGemvSum>(sign2, sel), lane, sink);
+            {
+                const TokenSinkN<NT> sink{acc, J.x0, J.xoff, J.ntiles, ch * 256};
+                if (refined) decode_words<true, RC, BK>(wb, wr, k, sink);
+                else decode_words<false, 0, BK>(wb, wr, k, sink);
+            }
+            st = st + kGemvStage == ring + kDepth * kGemvStage ? ring : st + kGemvStage;
         }
     }
     cp_async_wait<0>();
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[nt][i] = acc[nt][i];
+    return ok;
 }
 
 // 4 consecutive elements k = 4 lane + i of a 128-chunk -> operand order (two 4-byte stores)
@@ -334,8 +417,7 @@ __device__ __forceinline__ void rotate_piece(const MoeArgs& a, const Shape& sh, 
             store4h_operand(dst + a.H + blk * 128, lane, vu);
         }
     }
-    __threadfence();
-    __syncwarp();
+    __syncwarp();                      // the lanes' stores happen before lane 0's release below
     if (lane == 0) add_acq_rel(a.wq + 2, 1);
 }
 
@@ -343,6 +425,7 @@ __device__ __forceinline__ void rotate_piece(const MoeArgs& a, const Shape& sh, 
 // (run, group) complete: WHT128, sv, (+ low rank), SwiGLU, su_d, WHT128 -> h, one token after the other.
 __device__ __forceinline__ void finish_gate_up(const MoeArgs& a, const Shape& sh, const Route& R, int r, int grp, int lane)
 {
+    __syncwarp();        // lane 0's acquiring arrival is ordered before every lane's loads below
     const RunRec run = R.runs[r];
     const int64_t* row = a.table + (int64_t)run.expert * kTableWidth;
     const int S = sh.S, N = 2 * a.I, KS = sh.KSg, ng = sh.ng;
@@ -420,7 +503,6 @@ __device__ __forceinline__ void finish_gate_up(const MoeArgs& a, const Shape& sh
     {
         // 512-wide rotation = H_4 (x) WHT128 / 2: the last of the hw/128 groups of a block combines their fp32 results
         const int nb = hw / 128, b0 = grp / nb * nb;
-        __threadfence();
         __syncwarp();
         int last = 0;
         if (lane == 0)
@@ -433,6 +515,7 @@ __device__ __forceinline__ void finish_gate_up(const MoeArgs& a, const Shape& sh
         done = 0;
         if (last)
         {
+            __syncwarp();
             const float rs = rsqrtf((float)nb);
             for (int task = 0; task < run.count * nb; ++task)
             {
@@ -454,7 +537,6 @@ __device__ __forceinline__ void finish_gate_up(const MoeArgs& a, const Shape& sh
     }
     if (done)
     {
-        __threadfence();
         __syncwarp();
         if (lane == 0) add_acq_rel(a.cnt_gu + 2 * S * ng + r, done);
     }
@@ -463,6 +545,7 @@ __device__ __forceinline__ void finish_gate_up(const MoeArgs& a, const Shape& sh
 // output rows [grp * 128, +128) of token b are complete in every k-slice of every pick: weighted combine
 __device__ __forceinline__ void finish_down(const MoeArgs& a, const Shape& sh, const Route& R, int b, int grp, int lane)
 {
+    __syncwarp();        // the acquiring arrival (some lane's) is ordered before every lane's loads below
     const int S = sh.S, N = a.H, KS = sh.KSd, col = grp * 128 + lane * 4;
     float o[4] = {0.f, 0.f, 0.f, 0.f};
     for (int k = 0; k < a.topk; ++k)
@@ -512,37 +595,31 @@ __device__ __forceinline__ void finish_down(const MoeArgs& a, const Shape& sh, c
 // part[ks][slot][row].  false = a wait ran out.
 template <int NT>
 __device__ __forceinline__ bool gemv_piece(const MoeArgs& a, const Shape& sh, const Route& R, const RunRec& run, int DOWN, int strip, int c0, int c1,
-                                           int up, int ks, const int* gate_counter, int gate_target, uint8_t* ring, int lane)
+                                           int up, int ks, const int* gate_counter, int gate_target, uint32_t ring, int lane)
 {
     const int g = lane >> 2, t4 = lane & 3;
-    const int N = DOWN ? a.H : 2 * a.I, K = DOWN ? a.I : a.H, C = K / 128, NS = N / 16;
+    const int N = DOWN ? a.H : 2 * a.I, K = DOWN ? a.I : a.H;
     const int64_t* row = a.table + (int64_t)run.expert * kTableWidth;
-    const ProjPlanes P = planes_from_row(row, DOWN);
     const int rc = (int)row[10 + DOWN], nm = DOWN ? a.nm_dn : a.nm_gu, bk = (int)(row[19] >> (8 * DOWN)) & 0xFF;
     const bool level4 = run.level >= 4;
-    const StripRef sr = locate_strip(P, strip, C, NS, nm, level4);
-    const int ntiles = (run.count + 7) >> 3;
-    const uint8_t* xp[NT];
+    StripJob J;
+    J.P = planes_from_row(row, DOWN);
+    J.C = K / 128; J.NS = N / 16; J.c0 = c0; J.c1 = c1;
+    J.sr = locate_strip(J.P, strip, J.C, J.NS, nm, level4);
+    J.ntiles = (run.count + 7) >> 3;
+    J.has_token = g < run.count;
+    J.x0 = (const uint8_t*)(DOWN ? a.h : a.xrot);
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+    for (int nt = 0; nt < kRunTiles; ++nt)
     {
         const int j = nt * 8 + g;
-        const __half* rowp = nullptr;
-        if (j < run.count)
-        {
-            const int slot = R.order[run.first + j];
-            rowp = DOWN ? a.h + (size_t)slot * a.I : a.xrot + ((size_t)slot * 2 + up) * a.H;
-        }
-        xp[nt] = rowp ? (const uint8_t*)rowp + t4 * 64 : nullptr;
+        const int slot = R.order[run.first + (j < run.count ? j : 0)];
+        J.xoff[nt] = (uint32_t)((DOWN ? (size_t)slot * a.I : ((size_t)slot * 2 + up) * a.H) * 2 + t4 * 64);
     }
+    J.ring = ring; J.gate = gate_counter; J.gate_target = gate_target; J.status = a.status;
     float acc[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
     bool ok = true;
-    auto gate = [&]() { if (gate_counter) ok = wait_counter(gate_counter, gate_target, a.status); };
-#define NQ_RUN(RES, RCV, BKV) strip_gemv<RES, RCV, BKV, NT>(P, sr, C, NS, c0, c1, lane, acc, xp, ntiles, ring, gate)
+#define NQ_RUN(RES, RCV, BKV) ok = strip_gemv<RES, RCV, BKV, NT>(J, acc)
     NQ_WITH_CODES(level4, rc, bk, NQ_GEMV_CODES, NQ_RUN);
 #undef NQ_RUN
     if (!ok) return false;
@@ -573,7 +650,7 @@ __device__ __forceinline__ Shape make_shape(const MoeArgs& a, int nruns)
 // persistent CTAs of independent warps
 __global__ void __launch_bounds__(kThreads, NQ_GEMV_MINBLOCKS) moe_decode_kernel(MoeArgs a)
 {
-    extern __shared__ __align__(16) uint8_t smem_ring[];   // [kWarps][kDepth][kStageBytes]
+    extern __shared__ __align__(16) uint8_t smem_ring[];   // [kWarps][kDepth][kGemvStage]
     __shared__ Route R;
     launch_dependents();
     grid_dependency_wait();
@@ -591,18 +668,25 @@ __global__ void __launch_bounds__(kThreads, NQ_GEMV_MINBLOCKS) moe_decode_kernel
             if (R.nvalid[b] == 0)
                 for (int i = threadIdx.x; i < a.H; i += kThreads) a.out[(size_t)b * a.H + i] = 0.f;
 
-    uint8_t* ring = smem_ring + warp * (kDepth * kStageBytes);
+    const uint32_t ring = smem_addr(smem_ring) + warp * (kDepth * kGemvStage);
     const int total = sh.n_rot + sh.n_gu + sh.n_dn;
     bool rotated = false;      // this warp has seen every rotation piece finished
     int ready_run = -1;        // the run whose h this warp has seen complete
-    for (;;)
+    // a warp's first piece is its own index (thousands of warps start at once: no burst of atomics on one address); later
+    // ones come from the queue counter, which therefore counts from the number of warps
+    const int nwarps = (int)gridDim.x * kWarps;
+    for (int round = 0;; ++round)
     {
-        int piece = 0;
-        if (lane == 0) piece = atomicAdd(a.wq, 1);
-        else if (lane == 1) piece = ld_acquire(a.status);
-        const int raised = __shfl_sync(0xffffffffu, piece, 1);
-        piece = __shfl_sync(0xffffffffu, piece, 0);
-        if (piece >= total || raised) break;
+        int piece = (int)blockIdx.x * kWarps + warp;
+        if (round)
+        {
+            if (lane == 0) piece = nwarps + atomicAdd(a.wq, 1);
+            else if (lane == 1) piece = ld_acquire(a.status);
+            const int raised = __shfl_sync(0xffffffffu, piece, 1);
+            piece = __shfl_sync(0xffffffffu, piece, 0);
+            if (raised) break;
+        }
+        if (piece >= total) break;
         if (piece < sh.n_rot) { rotate_piece(a, sh, R, piece, lane); continue; }
         piece -= sh.n_rot;
         // gate|up: (run, group, gate / up, k-slice, strip of the group); down: (run, group, k-slice, strip of the group)
@@ -623,7 +707,8 @@ __global__ void __launch_bounds__(kThreads, NQ_GEMV_MINBLOCKS) moe_decode_kernel
         if (run.count <= 8) ok = gemv_piece<1>(a, sh, R, run, down, strip, c0, c1, up, ks, gate, target, ring, lane);
         else ok = gemv_piece<kRunTiles>(a, sh, R, run, down, strip, c0, c1, up, ks, gate, target, ring, lane);
         if (!ok) break;
-        __threadfence();
+        // Every arrival below is an acq_rel atomic issued after this warp barrier: the barrier orders all lanes' partial-sum
+        // stores before it, the release half publishes them, the acquire half of the last arrival sees everybody's.
         __syncwarp();
         if (!down)
         {
@@ -677,7 +762,7 @@ __global__ void __launch_bounds__(kThreads, NQ_GEMV_MINBLOCKS) moe_decode_kernel
     }
 }
 
-constexpr int kGemvSmem = kWarps * kDepth * kStageBytes;
+constexpr int kGemvSmem = kWarps * kDepth * kGemvStage;
 constexpr int kMaxDevices = 64;
 
 // CTAs that fit on the current device at once (the kernel is persistent); the first call on a device also opts the kernel

@@ -23,9 +23,8 @@ struct TileSink
 // fetch the unit's records into the warp's stage, read them back and decode
 template <bool RES, int RC, int BK>
 __device__ __forceinline__ void decode_one(const ProjPlanes& P, const StripRef& sr, int ch, int C, int NS, uint32_t sign2, int lane,
-                                           uint8_t* st, const TileSink& sink)
+                                           uint32_t st, const TileSink& sink)
 {
-    const ByteSelect sel = byte_select(lane);
     RecordCursor<BK> cb;
     cb.init(P.base, (size_t)NS * C * 32, sr.unit0 + ch, lane);
     cb.copy(st, 0, lane);
@@ -43,10 +42,10 @@ __device__ __forceinline__ void decode_one(const ProjPlanes& P, const StripRef& 
     {
         RecordCursor<RC>::read(wr, st + kStageBase, lane);
         const uint32_t word = __ldg(P.d4 + sr.res0 + refined_before(sr, ch));
-        decode_unit<true, RC, BK, kSumDefault>(wb, wr, consts_level4<kSumDefault>(block_multipliers(word), word, sign2, sel), lane, sink);
+        decode_unit<true, RC, BK>(wb, wr, consts_level4(block_multipliers(word), word, sign2), lane, sink);
     }
     else
-        decode_unit<false, 0, BK, kSumDefault>(wb, wr, consts_level2<kSumDefault>(sign2, sel), lane, sink);
+        decode_unit<false, 0, BK>(wb, wr, consts_level2(sign2), lane, sink);
 }
 
 // grid (ceil(max_units / 8), n_experts, 2 = gate|up / down), 256 threads.  The records take the same road as in the
@@ -81,7 +80,7 @@ __global__ void __launch_bounds__(256) pf_decode_kernel(const int64_t* __restric
     const bool refined = chunk_refined(sr, ch);
     const uint32_t sign2 = P.var ? sign_mask(__ldg(P.var + sr.unit0 + ch), lane) : 0u;
     const TileSink sink{tile, lane >> 2, lane & 3};
-#define NQ_RUN(RES, RCV, BKV) decode_one<RES, RCV, BKV>(P, sr, ch, C, NS, sign2, lane, st, sink)
+#define NQ_RUN(RES, RCV, BKV) decode_one<RES, RCV, BKV>(P, sr, ch, C, NS, sign2, lane, smem_addr(st), sink)
     NQ_WITH_CODES(refined, rc, bk, 0x3FF, NQ_RUN);
 #undef NQ_RUN
     __syncwarp();

@@ -35,10 +35,6 @@ namespace nq {
 #define NQ_PF_GROUPS 2      // groups of 8 decode warps; group g takes the chunks c = g (mod groups) of its strips.  3 groups
                             // (24 decode warps at 72 registers) measured the same time as 2: the kernel runs at the power cap
 #endif
-#ifndef NQ_PF_SUM
-#define NQ_PF_SUM NQ_SUM    // how the decode warps add hash bytes (see nq_format.cuh)
-#endif
-constexpr int kPfSum = NQ_PF_SUM;
 constexpr int kPfGroups = NQ_PF_GROUPS;
 constexpr int kPfDecodeWarps = 8 * kPfGroups;
 constexpr int kPfAStages = 2 * kPfGroups;            // weight tiles in tensor memory: each unit fills two consecutive stages
@@ -279,9 +275,8 @@ struct UnitSink
 // other parity), i.e. k-blocks 4 i + 2 GROUP and + 1.  it_base = k-blocks of earlier items.  false = aborted.
 template <bool REFINED, int RC, int BK, class Mid>
 __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, const StripRef& sr, int C, int NS, int lane, int group,
-                                             uint32_t tmem_a, uint8_t* ring, PfShared* sh, uint32_t it_base, Mid& mid)
+                                             uint32_t tmem_a, uint32_t ring, PfShared* sh, uint32_t it_base, Mid& mid)
 {
-    const ByteSelect sel = byte_select(lane);
     // per-unit scalars of this warp's chunks, one chunk (group + kPfGroups * lane) per lane: ring signs and, for refined units,
     // the block word with its fp16 multiplier / addend (computed once here instead of by every lane of every unit)
     uint32_t var_b = 0, ac = 0, mbn = 0;
@@ -302,7 +297,7 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, const StripRef
     cb.init(P.base, (size_t)NS * C * 32, sr.unit0, lane);
     RecordCursor<RC> cr;
     if constexpr (REFINED) cr.init(P.p4, sr.res_nrec, sr.res0, lane);
-    auto issue = [&](int ch, uint8_t* st) {
+    auto issue = [&](int ch, uint32_t st) {
         cb.copy(st, ch, lane);
         if constexpr (REFINED)
             if (chunk_refined(sr, ch)) cr.copy(st + kStageBase, refined_before(sr, ch), lane);
@@ -320,7 +315,7 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, const StripRef
         if (ch + kPfGroups * (kPfRingDepth - 1) < C) issue(ch + kPfGroups * (kPfRingDepth - 1), ring + slot_in * kStageBytes);
         cp_async_commit();
         cp_async_wait<kPfRingDepth - 1>();
-        const uint8_t* st = ring + slot * kStageBytes;
+        const uint32_t st = ring + slot * kStageBytes;
         slot = slot + 1 == kPfRingDepth ? 0 : slot + 1;
         slot_in = slot_in + 1 == kPfRingDepth ? 0 : slot_in + 1;
         const uint32_t sign2 = sign_mask(__shfl_sync(0xffffffffu, var_b, i), lane);
@@ -333,10 +328,10 @@ __device__ __forceinline__ bool decode_strip(const ProjPlanes& P, const StripRef
         {
             const uint32_t acw = __shfl_sync(0xffffffffu, ac, i), mb = __shfl_sync(0xffffffffu, mbn, i);
             RecordCursor<RC>::read(wr, st + kStageBase, lane);
-            decode_unit<true, RC, BK, kPfSum>(wb, wr, consts_level4<kPfSum>(acw, mb, sign2, sel), lane, sink);
+            decode_unit<true, RC, BK>(wb, wr, consts_level4(acw, mb, sign2), lane, sink);
         }
         else
-            decode_unit<false, 0, BK, kPfSum>(wb, wr, consts_level2<kPfSum>(sign2, sel), lane, sink);
+            decode_unit<false, 0, BK>(wb, wr, consts_level2(sign2), lane, sink);
         if (i == 0) mid();      // the previous item's epilogue, once this item's first tiles are on their way
     }
     cp_async_wait<0>();
@@ -349,7 +344,7 @@ __device__ __forceinline__ bool decode_item(const ProjPlanes& P, int level, int 
 {
     const StripRef sr = locate_strip(P, strip, C, NS, nm, level >= 4);
     bool ok = true;
-#define NQ_RUN(REF, RCV, BKV) ok = decode_strip<REF, RCV, BKV>(P, sr, C, NS, lane, group, tmem_a, ring, sh, it_base, mid)
+#define NQ_RUN(REF, RCV, BKV) ok = decode_strip<REF, RCV, BKV>(P, sr, C, NS, lane, group, tmem_a, smem_addr(ring), sh, it_base, mid)
     NQ_WITH_CODES(level >= 4, rc, bk, 0x3FF, NQ_RUN);
 #undef NQ_RUN
     return ok;

@@ -4,8 +4,8 @@
 // call, graph-capturable, running sums in a device fp64 array, every touched entry mirrored to a host-mapped fp64 array
 // that the host diffs like the routing-hit counters; picks with weight 0 are skipped, calls on one layer are
 // stream-ordered so the sums need no atomics across calls.  Built for this library's decode limits (32 tokens, 256
-// picks) instead of the reference's 8 x 8: one warp per token for the squared norms, one thread per pick, the picks of
-// one expert summed in pick order by their first pick.
+// picks) instead of the reference's 8 x 8: one warp per token for the squared norms, then one thread per expert adds that
+// expert's picks in pick order.
 #include <cuda_bf16.h>
 
 #include "nq_common.cuh"
@@ -47,18 +47,15 @@ __global__ void __launch_bounds__(256) salience_kernel(const T* __restrict__ x, 
         s_val[tid] = (double)(w * w * xn[tid / topk]);
     }
     __syncthreads();
-    if (tid < n && s_exp[tid] >= 0)
+    // one thread per expert: walk the picks in pick order and add up those of this expert (a fixed order of additions,
+    // no election of a writer among the picks)
+    for (int e = tid; e < E; e += 256)
     {
-        const int e = s_exp[tid];
         double tot = 0.0;
-        bool first = true;
+        bool any = false;
         for (int j = 0; j < n; ++j)
-            if (s_exp[j] == e)
-            {
-                if (j < tid) { first = false; break; }
-                tot += s_val[j];
-            }
-        if (first)
+            if (s_exp[j] == e) { tot += s_val[j]; any = true; }
+        if (any)
         {
             const double a = acc[e] + tot;
             acc[e] = a;

@@ -18,21 +18,48 @@ namespace nq {
 
 constexpr int kStageBase = 512, kStageBytes = kStageBase + 768;
 
-__device__ __forceinline__ void cp_async16(void* dst, const void* src)
+// Shared-memory operands below are 32-bit shared-space addresses (smem_addr of a pointer), so that a stage position plus a
+// lane offset is one register and every piece of a record an immediate offset from it.
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src)
 {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
 }
-__device__ __forceinline__ void cp_async8(void* dst, const void* src)
+// the same with compile-time byte offsets on both addresses
+template <int DOFF, int SOFF>
+__device__ __forceinline__ void cp_async16_at(uint32_t dst, const void* src)
 {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+    asm volatile("cp.async.cg.shared.global [%0 + %2], [%1 + %3], 16;" ::"r"(dst), "l"(src), "n"(DOFF), "n"(SOFF));
 }
-__device__ __forceinline__ void cp_async4(void* dst, const void* src)
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src)
 {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds128(uint32_t a)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
 
 // pieces of a record of window code CODE and where they sit inside a stage part
 template <int CODE>
@@ -65,7 +92,8 @@ struct RecordCursor
         if constexpr (L::has16) { p16 = p + unit0 * 64 + (lane >> 1) * 4; p += nrec * 2; }
         if constexpr (L::T != 0) ptail = p + unit0 * (4 * L::T) + ((lane * L::T) >> 5) * 4;
     }
-    __device__ __forceinline__ void copy(uint8_t* st, int u, int lane) const
+    // st: shared-space address of the stage part that receives the record pieces
+    __device__ __forceinline__ void copy(uint32_t st, int u, int lane) const
     {
         if constexpr (L::n128) cp_async16(st + L::o128 + lane * 16, p128 + (size_t)u * 512);
         if constexpr (L::has64) cp_async8(st + L::o64 + lane * 8, p64 + (size_t)u * 256);
@@ -79,23 +107,23 @@ struct RecordCursor
         }
     }
     // the lane's record as stream words w[0 .. kWords), bits past the record zero
-    static __device__ __forceinline__ void read(uint32_t* w, const uint8_t* st, int lane)
+    static __device__ __forceinline__ void read(uint32_t* w, uint32_t st, int lane)
     {
         int k = 0;
-        if constexpr (L::n128) { const uint4 v = *(const uint4*)(st + L::o128 + lane * 16); w[k++] = v.x; w[k++] = v.y; w[k++] = v.z; w[k++] = v.w; }
-        if constexpr (L::has64) { const uint2 v = *(const uint2*)(st + L::o64 + lane * 8); w[k++] = v.x; w[k++] = v.y; }
-        if constexpr (L::has32) w[k++] = *(const uint32_t*)(st + L::o32 + lane * 4);
-        if constexpr (L::has16) w[k++] = __byte_perm(*(const uint32_t*)(st + L::o16 + lane * 4), 0u, (lane & 1) ? 0x4432 : 0x4410);
+        if constexpr (L::n128) { const uint4 v = lds128(st + L::o128 + lane * 16); w[k++] = v.x; w[k++] = v.y; w[k++] = v.z; w[k++] = v.w; }
+        if constexpr (L::has64) { const uint2 v = lds64(st + L::o64 + lane * 8); w[k++] = v.x; w[k++] = v.y; }
+        if constexpr (L::has32) w[k++] = lds32(st + L::o32 + lane * 4);
+        if constexpr (L::has16) w[k++] = __byte_perm(lds32(st + L::o16 + lane * 4), 0u, (lane & 1) ? 0x4432 : 0x4410);
         if constexpr (L::T != 0)
         {
             const int sh = (lane * L::T) & 31;
             uint32_t v;
             if constexpr (L::tail2)
             {
-                const uint2 t = *(const uint2*)(st + L::otail + lane * 8);
+                const uint2 t = lds64(st + L::otail + lane * 8);
                 v = __funnelshift_r(t.x, t.y, sh);
             }
-            else v = *(const uint32_t*)(st + L::otail + lane * 4) >> sh;
+            else v = lds32(st + L::otail + lane * 4) >> sh;
             v &= (1u << L::T) - 1u;
             if constexpr (L::tail_joins) w[k - 1] |= v << 16;
             else w[k++] = v;

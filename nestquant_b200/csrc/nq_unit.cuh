@@ -34,20 +34,28 @@ __device__ __forceinline__ int refined_before(const StripRef& s, int ch)
 // ring sign of this lane's ring (bit g of the unit's sign byte) as an fp16x2 xor mask
 __device__ __forceinline__ uint32_t sign_mask(uint32_t var_byte, int lane) { return ((var_byte >> (lane >> 2)) & 1u) * 0x80008000u; }
 
-// Decode the lane's 64 weights of a unit whose record words are in registers (wb: kWords + 2 words of the base record,
-// wr: of the residual record).  sink(integral_constant<T>, a[4]) receives, for k-step T = 0..7, the m16n8k16
-// A-fragment registers: a[q] = rows g + 8 (q & 1), k = 16 T + 2 t4 + 8 (q >> 1) + {0, 1}.  Called by whole warps.
-template <bool RES, int RC, int BK, int SUM, class Sink>
+// Decode the lane's 64 weights of a unit whose stream words are in registers (wb: the base record, wr: the residual record,
+// each already continued with the ring successor's first word: kWords + 2 words).  sink(integral_constant<T>, a[4])
+// receives, for k-step T = 0..7, the m16n8k16 A-fragment registers: a[q] = rows g + 8 (q & 1),
+// k = 16 T + 2 t4 + 8 (q >> 1) + {0, 1}.
+template <bool RES, int RC, int BK, class Sink>
+__device__ __forceinline__ void decode_words(const uint32_t* wb, const uint32_t* wr, const UnitConsts& k, Sink&& sink)
+{
+    static_for<8>([&](auto tc) {
+        uint32_t a[4];
+        decode_kstep<RES, RC, BK, decltype(tc)::value>(wb, wr, k, a);
+        sink(tc, a);
+    });
+}
+// The same for record words as read from the planes: fetches the continuation words from the ring successors first.
+// Called by whole warps.
+template <bool RES, int RC, int BK, class Sink>
 __device__ __forceinline__ void decode_unit(uint32_t* wb, uint32_t* wr, const UnitConsts& k, int lane, Sink&& sink)
 {
     const int nxt = ring_successor(lane);
     continue_stream<Pattern<BK>::kBits>(wb, __shfl_sync(0xffffffffu, wb[0], nxt));
     if constexpr (RES) continue_stream<Pattern<RC>::kBits>(wr, __shfl_sync(0xffffffffu, wr[0], nxt));
-    static_for<8>([&](auto tc) {
-        uint32_t a[4];
-        decode_kstep<RES, RC, BK, decltype(tc)::value, SUM>(wb, wr, k, a);
-        sink(tc, a);
-    });
+    decode_words<RES, RC, BK>(wb, wr, k, sink);
 }
 
 // Base code 1 is built with the residual codes it ships with (3 for gate|up, 9 for down: sm120/NQ_RES_V2.md:9-13).
