@@ -87,6 +87,14 @@ int nq_promote(void* slot, const void* host_record, size_t record_bytes, int64_t
 int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const int64_t* table, int E, void* xg, void* xu, float* zg,
               int H, int I, int kperm, void* stream);
 
+/* The same pass when the tokens' input rows are spread over the ranks of an expert-parallel group: token t is row
+ * t % tokens_per_rank of peer_x[t / tokens_per_rank] (host array of `world` device addresses as seen from this GPU:
+ * symmetric memory / peer mappings; fp16 [tokens_per_rank][H] each).  Reading a pair's row from its owner is the dispatch
+ * step of the expert-parallel prefill, done by plain peer loads inside this kernel (the caller's nq_ep_barrier makes the
+ * peers' rows complete first).  No counterpart in the reference (its serving path is tensor-parallel). */
+int nq_pf_pre_ep(const void* const* peer_x, int world, int tokens_per_rank, const int32_t* pt, const int32_t* pe, int R,
+                 const int64_t* table, int E, void* xg, void* xu, float* zg, int H, int I, int kperm, void* stream);
+
 /* acc_g, acc_u fp32 [R][I] (GEMM outputs) -> h fp16 [R][I] = WHT_w(silu(g) u su_d), g = WHT128(acc_g) sv_g + low rank,
  * w = 128 or the expert's 512-wide rotation; zd[p][r] = (silu(g) u) . V_dn[r].  kperm: k order of h as for nq_pf_pre.
  * Replaces pf_mid() (sm120/nqmoe.cu:1118-1203,1268-1277). */
@@ -187,7 +195,8 @@ int nq_moe_forward(const NqMoeForward* args, void* stream);
  * (its workspaces are always torch tensors owned by the caller).  The workspaces of nq_moe_forward live in an array that
  * is part of the library image: nq_moe_static_scratch_bytes() = 4 MiB, held by every GPU that loads the library until
  * the process exits.  A call shape whose workspaces (nq_moe_workspace) do not fit is refused with NQ_ERR_ARG; 4 MiB
- * covers the GLM-5 shape up to 4 tokens x top-8.  The call issues no cudaMalloc / cudaFree and no allocating library
+ * covers the GLM-5 shape (H 6144, I 2048, top-8) for 1 token at any k-split up to (8, 4) and for up to 4 tokens at k-split
+ * (2, 1); 4 tokens at (4, 2) need 4.6 MB and are refused.  The call issues no cudaMalloc / cudaFree and no allocating library
  * routine.  The first call on a device looks up the array's device address (cudaGetSymbolAddress): make that call at
  * start-up, before any stream capture on the device.  All calls share the array, which keeps the previous call's
  * contents; the counters are cleared at the start of each call, and calls that overlap on the GPU race - keep them in
@@ -214,6 +223,16 @@ int nq_salience(const void* x, int x_is_bf16, int64_t row_stride, const void* rw
  * rows complete first.  No counterpart in the reference; it takes the place of the dispatch all-to-all. */
 int nq_ep_gather(void* xstage, const void* const* peer_x, const int64_t* sel, const void* rw, int tokens_per_rank, int topk, int H,
                  int world, int rank, int experts_per_rank, void* stream);
+
+/* Barrier over the ranks of an expert-parallel group, as one small kernel per rank on `stream`: rank `rank` stores its call
+ * number (*epoch + 1) into flag [rank] of every peer_flags[r] (int32 [world] per rank, zero-initialised symmetric memory;
+ * host array of `world` device addresses as seen from this GPU), waits until its own flags have all reached that number,
+ * then advances *epoch (device int32, zero-initialised, private to this rank and this group of buffers).  Everything the
+ * stream wrote before the barrier is visible to the peers' kernels after theirs.  The wait is bounded by timeout_ns: when
+ * it runs out *status (device int32) is set to 1 and the kernel returns - read it after synchronising.  Graph-capturable
+ * (the call number is read on the device).  No counterpart in the reference. */
+int nq_ep_barrier(int32_t* const* peer_flags, int rank, int world, int32_t* epoch, int32_t* status, long long timeout_ns,
+                  void* stream);
 
 /* Expert-parallel combine over peer memory: out[t] (fp32 [T][H]) = sum over the ranks r = 0 .. world - 1, in that order,
  * of row rows[r * T + t] (int32, -1 = none) of peer_parts[r] (fp32 [.][H], device addresses of every rank's partial-row

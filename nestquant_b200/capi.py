@@ -56,6 +56,7 @@ SIGNATURES = {
     "nq_mailbox": (_i, [_p, _p, _p, _p, _p, _i, _p]),
     "nq_promote": (_i, [_p, _p, _sz, _p, _p, _p, _p, _p]),
     "nq_pf_pre": (_i, [_p, _p, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _p]),
+    "nq_pf_pre_ep": (_i, [C.POINTER(_p), _i, _i, _p, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _p]),
     "nq_pf_mid": (_i, [_p, _p, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _p]),
     "nq_pf_post": (_i, [_p, _p, _p, _p, _p, _i, _p, _i, _p, _i, _i, _p]),
     "nq_pf_combine": (_i, [_p, _p, _p, _p, _p, _i, _i, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
@@ -68,6 +69,7 @@ SIGNATURES = {
     "nq_moe_static_scratch_bytes": (_sz, []),
     "nq_moe_forward_static": (_i, [_p, _p, _p, _p, _p] + [_i] * 9 + [_p, _p]),
     "nq_salience": (_i, [_p, _i, _i64, _p, _p, _i, _i, _i, _i, C.c_float, _p, _p, _p]),
+    "nq_ep_barrier": (_i, [C.POINTER(_p), _i, _i, _p, _p, C.c_longlong, _p]),
     "nq_ep_gather": (_i, [_p, C.POINTER(_p), _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "nq_ep_combine": (_i, [_p, C.POINTER(_p), _p, _i, _i, _i, _p]),
     "nq_engine_open": (_i, [C.c_char_p, C.c_char_p, _sz, _i, _i, _i, _i, C.POINTER(_p)]),

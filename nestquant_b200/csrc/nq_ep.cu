@@ -1,17 +1,24 @@
 // Expert-parallel exchange over peer memory (plain peer loads over NVLink, no collective on the data path).
 //
-// Dispatch: every rank keeps its tokens' input rows in a symmetric buffer; nq_ep_gather copies, into a local staging
-// matrix indexed by global token, the rows of exactly those tokens that picked one of this rank's experts (each row
-// crosses NVLink once per destination rank, as in an all-to-all, but pulled by the consumer and without any size
-// exchange on the host).
+// Dispatch: every rank keeps its tokens' input rows in a symmetric buffer.  The prefill's first pass (nq_pf_pre with
+// peer row pointers, nq_prefill.cu) reads the row of each of its pairs straight from the owner's buffer while it scales and
+// rotates it: the dispatch is part of that kernel.  nq_ep_gather is the stand-alone form (a staging matrix indexed by
+// global token gets the rows of exactly those tokens that picked one of this rank's experts).
 // Combine: out[t] = sum over the ranks r, in rank order, of the partial row rank r computed for token t, read straight
 // from rank r's buffer.
 //
 // This is the return leg of the expert-parallel prefill (the reference names the exchange, sm120/eval/eval_reg.py:137-142;
 // its serving path is tensor-parallel and has no counterpart kernel): instead of an all-to-all of the partial rows into a
 // receive buffer followed by an indexed add, the owner of a token gathers and sums its partial rows in one pass.  The
-// buffers are symmetric-memory allocations whose peer addresses the host passes in; the host brackets the call with the
-// barriers that make the peers' rows complete before and keep them untouched during the reads.
+// buffers are symmetric-memory allocations whose peer addresses the host passes in; the host brackets the call with
+// nq_ep_barrier, which makes the peers' rows complete before and keeps them untouched during the reads.
+//
+// Barrier: one small kernel per rank.  Rank r stores its call number into flag [r] of every peer (release, system scope)
+// and waits until all of its own flags have reached that number (acquire, system scope).  The wait is bounded: when it
+// runs out the kernel raises a status word and returns, so a peer that died or never arrives cannot hang this GPU.  The
+// call number lives in device memory and is advanced by the kernel itself, so the call can be replayed from a CUDA graph.
+// The kernels of different ranks run on different GPUs; never launch two ranks' barriers on one GPU and expect them to
+// meet.
 #include <cuda_fp16.h>
 
 #include "nq_common.cuh"
@@ -61,7 +68,57 @@ __global__ void __launch_bounds__(128) ep_gather_kernel(__half* __restrict__ xst
     for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 
+struct EpFlags { int32_t* flags[kEpMaxRanks]; };
+
+__global__ void __launch_bounds__(32) ep_barrier_kernel(EpFlags peers, int rank, int world, int32_t* epoch, int32_t* status,
+                                                        unsigned long long timeout_ns)
+{
+    const int r = threadIdx.x;
+    const int32_t e = *(volatile int32_t*)epoch + 1;
+    __syncwarp();
+    bool ok = true;
+    if (r < world)
+    {
+        __threadfence_system();       // everything this GPU wrote before the barrier is visible to the peers first
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peers.flags[r] + rank), "r"(e) : "memory");
+        const int32_t* mine = peers.flags[rank] + r;
+        unsigned long long t0 = 0;
+        for (unsigned i = 0;; ++i)
+        {
+            int32_t v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (v - e >= 0) break;
+            if ((i & 15u) == 15u)
+            {
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                if (t0 == 0) t0 = t;
+                else if (t - t0 > timeout_ns) { ok = false; break; }
+            }
+            __nanosleep(200);
+        }
+    }
+    if (!ok) atomicExch(status, 1);
+    __syncwarp();
+    if (r == 0) *epoch = e;
+}
+
 }  // namespace nq
+
+extern "C" int nq_ep_barrier(int32_t* const* peer_flags, int rank, int world, int32_t* epoch, int32_t* status, long long timeout_ns,
+                             void* stream)
+{
+    NQ_REQUIRE(world >= 1 && world <= nq::kEpMaxRanks && rank >= 0 && rank < world, "nq_ep_barrier: rank %d of %d", rank, world);
+    NQ_REQUIRE(peer_flags && epoch && status && timeout_ns > 0, "nq_ep_barrier: null pointer or timeout %lld", timeout_ns);
+    nq::EpFlags f{};
+    for (int r = 0; r < world; ++r)
+    {
+        NQ_REQUIRE(peer_flags[r], "nq_ep_barrier: flags of rank %d are null", r);
+        f.flags[r] = peer_flags[r];
+    }
+    nq::ep_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, rank, world, epoch, status, (unsigned long long)timeout_ns);
+    return nq::check_launch("nq_ep_barrier");
+}
 
 extern "C" int nq_ep_gather(void* xstage, const void* const* peer_x, const int64_t* sel, const void* rw, int tokens_per_rank, int topk, int H,
                             int world, int rank, int experts_per_rank, void* stream)

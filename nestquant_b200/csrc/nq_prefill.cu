@@ -45,8 +45,20 @@ __device__ __forceinline__ float quad_sum(float d)
     d += __shfl_xor_sync(0xffffffffu, d, 1);
     return d + __shfl_xor_sync(0xffffffffu, d, 2);
 }
+// Where the input rows live: token t is row t % tokens_per_rank of buffer t / tokens_per_rank.  One buffer holding every
+// token is the single-GPU case; under expert parallelism the buffers are the ranks' symmetric-memory input buffers as seen
+// from this GPU, and reading a row IS the dispatch (plain peer loads over NVLink, each pair's row fetched by the rank that
+// multiplies it).
+constexpr int kPfMaxRanks = 8;
+struct TokenRows { const __half* base[kPfMaxRanks]; int tokens_per_rank; };
+__device__ __forceinline__ const __half* token_row(const TokenRows& r, int t, int H)
+{
+    const int owner = t / r.tokens_per_rank;
+    return r.base[owner] + (size_t)(t - owner * r.tokens_per_rank) * H;
+}
+
 // one CTA per pair, one warp per 1024 columns
-__global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(const __half* __restrict__ x, const int* __restrict__ pt, const int* __restrict__ pe,
+__global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(TokenRows rows, const int* __restrict__ pt, const int* __restrict__ pe,
                                                      const int64_t* __restrict__ table, int E, __half* xg, __half* xu, float* zg, int H, int I, int kperm)
 {
     const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -56,7 +68,7 @@ __global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(const __ha
     if (level <= 0) return;
     const __half* scales = (const __half*)row[9];
     const __half* su_u = scales + 2 * H + 3 * I;
-    const __half* xr = x + (size_t)pt[p] * H;
+    const __half* xr = token_row(rows, pt[p], H);
     const int ng = H / 128;
     for (int g0 = warp * 8; g0 < ng; g0 += nwarp * 8)
     {
@@ -308,8 +320,31 @@ int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const 
     NQ_SHAPE_OK("nq_pf_pre");
     NQ_REQUIRE(E >= 1, "nq_pf_pre: E = %d", E);
     NQ_REQUIRE(nq::aligned16(x) && nq::aligned16(xg) && nq::aligned16(xu), "nq_pf_pre: x, xg, xu must be 16-byte aligned");
-    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>((const __half*)x, pt, pe, table, E, (__half*)xg, (__half*)xu, zg, H, I, kperm);
+    nq::TokenRows rows{};
+    rows.base[0] = (const __half*)x; rows.tokens_per_rank = 0x7fffffff;
+    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>(rows, pt, pe, table, E, (__half*)xg, (__half*)xu, zg, H, I, kperm);
     return nq::check_launch("nq_pf_pre");
+}
+
+int nq_pf_pre_ep(const void* const* peer_x, int world, int tokens_per_rank, const int32_t* pt, const int32_t* pe, int R, const int64_t* table, int E,
+                 void* xg, void* xu, float* zg, int H, int I, int kperm, void* stream)
+{
+    NQ_REQUIRE(R >= 0, "nq_pf_pre_ep: R = %d", R);
+    if (R == 0) return NQ_OK;
+    NQ_REQUIRE(peer_x && pt && pe && table && xg && xu && zg, "nq_pf_pre_ep: null pointer");
+    NQ_REQUIRE(world >= 1 && world <= nq::kPfMaxRanks && tokens_per_rank >= 1, "nq_pf_pre_ep: world = %d, tokens per rank = %d", world, tokens_per_rank);
+    NQ_SHAPE_OK("nq_pf_pre_ep");
+    NQ_REQUIRE(E >= 1, "nq_pf_pre_ep: E = %d", E);
+    NQ_REQUIRE(nq::aligned16(xg) && nq::aligned16(xu), "nq_pf_pre_ep: xg, xu must be 16-byte aligned");
+    nq::TokenRows rows{};
+    for (int r = 0; r < world; ++r)
+    {
+        NQ_REQUIRE(peer_x[r] && nq::aligned16(peer_x[r]), "nq_pf_pre_ep: input buffer of rank %d is null or misaligned", r);
+        rows.base[r] = (const __half*)peer_x[r];
+    }
+    rows.tokens_per_rank = tokens_per_rank;
+    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>(rows, pt, pe, table, E, (__half*)xg, (__half*)xu, zg, H, I, kperm);
+    return nq::check_launch("nq_pf_pre_ep");
 }
 
 int nq_pf_mid(const float* acc_g, const float* acc_u, const float* zg, const int32_t* pe, int R, const int64_t* table, int E, void* h,

@@ -61,6 +61,19 @@ def pf_pre(x, pt, pe, table, xg, xu, zg, I, kperm=False):
     check(lib().nq_pf_pre(ptr(x), ptr(pt), ptr(pe), R, ptr(table), table.shape[0], ptr(xg), ptr(xu), ptr(zg), H, I, int(bool(kperm)), current_stream()), "pf_pre")
 
 
+def pf_pre_ep(peer_ptrs, tokens_per_rank, H, pt, pe, table, xg, xu, zg, I, kperm=False):
+    """pf_pre with the input rows read from the ranks' buffers: peer_ptrs = device addresses (ints) of every rank's fp16
+    [tokens_per_rank, H] input buffer as seen from this GPU; pt holds global token ids (rank * tokens_per_rank + t)"""
+    _need(pt, torch.int32, "pt"); _need(pe, torch.int32, "pe"); _need(table, torch.int64, "table")
+    _need(xg, torch.float16, "xg"); _need(xu, torch.float16, "xu"); _need(zg, torch.float32, "zg")
+    R = pt.numel()
+    if pe.numel() < R or xg.numel() < R * H or xu.numel() < R * H or zg.numel() < R * 4:
+        raise NestQuantError("pf_pre_ep sizes")
+    arr = (C.c_void_p * len(peer_ptrs))(*peer_ptrs)
+    check(lib().nq_pf_pre_ep(arr, len(peer_ptrs), tokens_per_rank, ptr(pt), ptr(pe), R, ptr(table), table.shape[0], ptr(xg), ptr(xu),
+                             ptr(zg), H, I, int(bool(kperm)), current_stream()), "pf_pre_ep")
+
+
 def pf_mid(acc_g, acc_u, zg, pe, table, h, zd, H, I, kperm=False):
     """acc_g / acc_u fp32 [R,I] -> h fp16 [R,I] (rotations, scales, SwiGLU), zd [R,4]"""
     _need(acc_g, torch.float32, "acc_g"); _need(acc_u, torch.float32, "acc_u"); _need(zg, torch.float32, "zg")

@@ -370,7 +370,7 @@ class MoELayer:
             body()
         return g
 
-    def prefill(s, x, sel, rw, out=None, R=None, G=None, table=None):
+    def prefill(s, x, sel, rw, out=None, R=None, G=None, table=None, x_peers=None):
         """T > Bmax tokens: pairs (token, pick) sorted by expert, each routed expert decoded inside the grouped GEMM (tcgen05 /
         TMEM; dense weights never touch HBM), same math as __call__.  x fp16 [T,H], sel int64 [T,topk], rw fp16 [T,topk] ->
         fp32 [T,H].  Same call shape as the reference's prefill (sm120/moe.py:282-327).
@@ -379,11 +379,14 @@ class MoELayer:
         token's picks are added chunk after chunk in pick order, so the result is bitwise repeatable for a given R.
         G (experts decoded per group in the reference) is accepted and ignored: nothing is decoded ahead of the GEMM.
         Picks whose expert id is outside [0, E) (e.g. -1 padding) are ignored, as on the decode path.
+        x_peers = (device addresses of every rank's input buffer, tokens per rank): expert parallelism - x is ignored (pass
+        any fp16 [*, H] tensor on the device), token t of sel / rw is read from buffer t // tokens_per_rank by the first pass
+        itself (see nq_pf_pre_ep).
         Nothing here synchronises with the host; a device-side time-out inside the GEMM raises a flag that
         prefill_status() reads."""
         assert x.dtype == torch.float16 and rw.dtype == torch.float16 and sel.dtype == torch.int64, (x.dtype, rw.dtype, sel.dtype)
         T, k = sel.shape
-        H, I, E, M, dev = s.H, s.I, s.E, s.M, x.device
+        H, I, E, M, dev = s.H, s.I, s.E, s.M, sel.device
         tb = s.table if table is None else table
         P = T * k
         R = max(1, min(R or 65536, P))
@@ -415,7 +418,10 @@ class MoELayer:
             cnt_c = (torch.clamp(end, max=c0 + n) - torch.clamp(start, min=c0)).clamp_(min=0)[:E].contiguous()
             M.pf_plan(cnt_c, tb, sc["plan"], n)
             xg, xu, y = sc["xg"][:n], sc["xu"][:n], sc["y"][:n]
-            M.pf_pre(x, pt[c0:c0 + n], pe[c0:c0 + n], tb, xg, xu, sc["zg"], I, kperm=True)
+            if x_peers is None:
+                M.pf_pre(x, pt[c0:c0 + n], pe[c0:c0 + n], tb, xg, xu, sc["zg"], I, kperm=True)
+            else:
+                M.pf_pre_ep(x_peers[0], x_peers[1], H, pt[c0:c0 + n], pe[c0:c0 + n], tb, xg, xu, sc["zg"], I, kperm=True)
             M.pf_gemm(tb, sc["plan"], xg, xu, sc["acc_g"], sc["acc_u"], H, I, s.nm_gu, s.nm_dn, False, sc["status"])
             M.pf_mid(sc["acc_g"], sc["acc_u"], sc["zg"], pe[c0:c0 + n], tb, sc["h"], sc["zd"], H, I, kperm=True)
             M.pf_gemm(tb, sc["plan"], sc["h"][:n], None, y, None, H, I, s.nm_gu, s.nm_dn, True, sc["status"])     # y overwrites xg | xu
@@ -426,6 +432,9 @@ class MoELayer:
         """scratch of the prefill path for chunks of R pairs, kept between calls (the reference's pf_scratch,
         sm120/moe.py:263-275, without its dense weight buffers): xg | xu fp16 [R,H] each, aliased by y fp32 [R,H];
         acc_g, acc_u fp32 [R,I]; h fp16 [R,I]; zg, zd fp32 [R,4]; the pass list; the status word"""
+        owner = getattr(s, "_pf_owner", None)
+        if owner is not None:
+            return owner._prefill_scratch(R, dev)
         sc = getattr(s, "_pf_sc", None)
         if sc is not None and sc["R"] == R and sc["y"].device == dev:
             return sc
@@ -441,9 +450,18 @@ class MoELayer:
                         plan=torch.empty(s.M.pf_plan_ints(E, R), dtype=i32, device=dev), status=status)
         return s._pf_sc
 
+    def share_prefill_scratch(s, other):
+        """use the prefill scratch (and status word) of another layer of the same shape: the layers of a stack run one after
+        the other on one stream, so one set of buffers serves them all"""
+        assert (other.H, other.I, other.E) == (s.H, s.I, s.E)
+        s._pf_owner = other
+
     def prefill_status(s):
         """0, or 1 if a device-side wait inside the prefill GEMM has run out since the layer was built (results of that call are
         invalid).  Synchronises with the device."""
+        owner = getattr(s, "_pf_owner", None)
+        if owner is not None:
+            return owner.prefill_status()
         sc = getattr(s, "_pf_sc", None)
         return 0 if sc is None else int(sc["status"].item())
 

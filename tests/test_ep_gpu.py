@@ -1,7 +1,8 @@
 """Expert-parallel layer on 2 GPUs (skipped on a single-GPU box): the prefill whose exchange runs over peer memory (input
-rows pulled by nq_ep_gather, partial rows summed by nq_ep_combine from the peers' symmetric-memory buffers) must equal, bit
-for bit, the all-to-all + indexed-add path, and both must match a single-GPU layer holding every expert; decode =
-replicated tokens + all-reduce."""
+rows read from their owners by the first prefill pass, partial rows summed by nq_ep_combine from the peers'
+symmetric-memory buffers, nq_ep_barrier in between) must equal, bit for bit, the all-to-all + indexed-add path, and both
+must match a single-GPU layer holding every expert; decode = replicated tokens + all-reduce.  The exchange kernels and the
+bounded barrier are also tested on one GPU with emulated ranks."""
 import os
 
 import pytest
@@ -43,6 +44,7 @@ def _worker(rank, world, port, q):
         y_peer2 = ep_peer.prefill(xr, selr, rwr)
         torch.cuda.synchronize()
         res = dict(peer_on=ep_peer.peer is not None, combine=ep_peer.last_stats.get("combine"), dispatch=ep_peer.last_stats.get("dispatch"),
+                   timed_out=ep_peer.peer is not None and ep_peer.peer.timed_out(),
                    same=bool(torch.equal(y_a2a, y_peer)) and bool(torch.equal(y_peer, y_peer2)),
                    err=layer_errors(y_peer.cpu().numpy(), ref.cpu().numpy())[1])
         xd, seld, rwd = x[:3].to(dev), sel[:3].to(dev), rw[:3].to(dev)
@@ -73,7 +75,7 @@ def test_prefill_combine_over_peer_memory():
     out = dict(q.get(timeout=10) for _ in range(2))
     for rank, r in out.items():
         assert r["peer_on"] and r["combine"] == "peer loads" and r["dispatch"] == "peer loads", (rank, r)
-        assert r["same"] and r["err"] <= 1e-4 and r["decode_err"] <= 1e-4, (rank, r)
+        assert r["same"] and r["err"] <= 1e-4 and r["decode_err"] <= 1e-4 and not r["timed_out"], (rank, r)
         assert r["decode_peer_err"] <= 1e-4 and r["decode_peer_same"], (rank, r)
 
 
@@ -107,3 +109,56 @@ def test_exchange_kernels_on_one_gpu():
         ref = ref + torch.where(ok[:, None], parts[r][rows[r].clamp(min=0).long()], torch.zeros_like(ref))
     torch.cuda.synchronize()
     assert torch.equal(out, ref)
+
+
+def test_barrier_wait_is_bounded_and_prefill_first_pass_reads_peer_rows():
+    """nq_ep_barrier on one GPU, as rank 0 of 2: with the peer's flag already at the call number the barrier passes and the
+    call number advances; with a flag that nothing sets the wait runs out after its (short) limit, the status word is raised
+    and the kernel returns - the device stays usable.  Then nq_pf_pre_ep with the buffers of three emulated ranks on this
+    device (the kernel only sees addresses) against nq_pf_pre on the concatenated rows."""
+    import ctypes as C
+    import time
+    from nestquant_b200 import ext, moe
+    from nestquant_b200.capi import check, lib
+    st = torch.cuda.current_stream().cuda_stream
+    mine = torch.zeros(8, dtype=torch.int32, device="cuda")          # my flags: [r] = what rank r announced to me
+    theirs = torch.zeros(8, dtype=torch.int32, device="cuda")        # the emulated peer's flags
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flags = (C.c_void_p * 2)(mine.data_ptr(), theirs.data_ptr())
+    mine[1] = 1                                                      # the peer has announced call 1 already
+    check(lib().nq_ep_barrier(flags, 0, 2, epoch.data_ptr(), status.data_ptr(), 50_000_000, st), "ep_barrier")
+    torch.cuda.synchronize()
+    assert int(status) == 0 and int(epoch) == 1 and int(theirs[0]) == 1 and int(mine[0]) == 1
+    t = time.perf_counter()
+    check(lib().nq_ep_barrier(flags, 0, 2, epoch.data_ptr(), status.data_ptr(), 50_000_000, st), "ep_barrier")   # call 2: nobody answers
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t
+    assert int(status) == 1 and int(epoch) == 2 and int(theirs[0]) == 2, "the wait must give up and say so"
+    assert 0.03 < dt < 1.0, dt                                       # 50 ms limit
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0          # the context is alive
+
+    W, Tl, H, I, NE, topk = 3, 20, 512, 256, 6, 2
+    exs = [moe.Expert(H, I, seed=40 + i, sv=0.02) for i in range(NE)]
+    L = moe.MoELayer(NE, H, I, Bmax=1, topk=topk)
+    for e in range(NE):
+        L.set(e, exs[e], 2 if e != 4 else 0)
+    g = torch.Generator().manual_seed(5)
+    xs = [torch.randn(Tl, H, generator=g).half().cuda() for _ in range(W)]
+    R = W * Tl * topk
+    pt = torch.randint(0, W * Tl, (R,), generator=g).int().cuda()
+    pe = torch.randint(-1, NE + 1, (R,), generator=g).int().cuda()     # includes ids outside [0, E) and a level-0 expert
+    outs = []
+    for peers in (False, True):
+        xg = torch.full((R, H), 3.0, dtype=torch.float16, device="cuda")
+        xu = torch.full((R, H), 3.0, dtype=torch.float16, device="cuda")
+        zg = torch.zeros(R, 4, device="cuda")
+        if peers:
+            ext.pf_pre_ep([x.data_ptr() for x in xs], Tl, H, pt, pe, L.table, xg, xu, zg, I, kperm=True)
+        else:
+            ext.pf_pre(torch.cat(xs), pt, pe, L.table, xg, xu, zg, I, kperm=True)
+        outs.append((xg, xu))
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    skipped = (pe < 0) | (pe >= NE) | (pe == 4)
+    assert bool((outs[1][0][skipped] == 3.0).all()) and bool((outs[1][0][~skipped] != 3.0).any())

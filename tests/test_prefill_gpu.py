@@ -119,6 +119,26 @@ def test_prefill_glm_shape_fused_matches_library_gemm():
     assert layer_errors((2 * yh).cpu().numpy(), y.cpu().numpy())[1] <= 1e-3      # halving fp16 weights is exact up to subnormals
 
 
+def test_prefill_glm_shape_against_the_oracle():
+    """Full-size expert shape (H 6144, I 2048, top-8): 1024 tokens through the fused prefill, 24 of them (every expert level
+    and the masked experts among their picks) checked against the CPU oracle, which decodes the whole experts."""
+    from nestquant_b200 import synth
+    from tests.util import layer_report
+    cfg = dict(synth.GLM); cfg["E"] = 12
+    levels = [4] * 7 + [2] * 4 + [0]
+    L, experts = synth.build_layer(cfg, levels, seed=21, Bmax=1, masked={2, 5})
+    T, S = 1024, 24
+    sel, rw = synth.routing(T, cfg["E"], cfg["topk"], 22)
+    x = synth.tokens(T, cfg["H"], 23)
+    y = L.prefill(x.cuda(), sel.cuda(), rw.cuda())
+    torch.cuda.synchronize()
+    assert L.prefill_status() == 0
+    exs_o = [expert_to_oracle(experts[e]) if e in experts else None for e in range(cfg["E"])]
+    ref = O.moe_ref(exs_o, levels, x[:S].numpy(), sel[:S].numpy(), rw[:S].numpy())
+    rep = layer_report(y[:S].cpu().numpy(), ref)
+    assert rep["max_abs_unit_rms"] <= MAX_ABS_TOL and rep["rel_l2"] <= REL_L2_TOL and rep["rel_l2"] <= 5e-4, rep
+
+
 def test_prefill_many_tokens_per_expert():
     """Experts with more tokens than one pass holds (384) and than one MMA is wide (256): several passes per expert,
     token tiles cut in two column halves; against the library-GEMM path and the oracle."""

@@ -73,6 +73,17 @@ def layer_errors(got: np.ndarray, ref: np.ndarray):
     return float(np.abs(d).max()) / scale, float(np.linalg.norm(d) / max(np.linalg.norm(ref64), 1e-30))
 
 
+def layer_report(got: np.ndarray, ref: np.ndarray) -> dict:
+    """every reading of the layer-output error at once: raw max |got - ref|, the same on unit-RMS outputs, relative L2,
+    and the RMS of the reference (so that the raw figure can be judged)"""
+    ref64 = ref.astype(np.float64)
+    d = got.astype(np.float64) - ref64
+    rms = float(np.sqrt((ref64 ** 2).mean()))
+    raw = float(np.abs(d).max()) if d.size else 0.0
+    return dict(max_abs_raw=raw, max_abs_unit_rms=raw / max(1.0, rms), rel_l2=float(np.linalg.norm(d) / max(np.linalg.norm(ref64), 1e-30)),
+                ref_rms=rms)
+
+
 # layer-output tolerance of the path (fp16 operands, fp32 accumulate-order tolerance): max-abs 1e-2 (on unit-RMS
 # outputs) and relative L2 2e-3
 MAX_ABS_TOL, REL_L2_TOL = 1e-2, 2e-3
