@@ -225,21 +225,17 @@ def prefill_pieces(L, x, sel, rw):
     T, k = sel.shape
     H, I, E, P, dev = L.H, L.I, L.E, T * k, x.device
     i32, f16, f32 = torch.int32, torch.float16, torch.float32
-    flat = sel.reshape(-1)
-    order = torch.argsort(flat, stable=True)
-    pe, pt = flat[order].to(i32), (order // k).to(i32)
-    cnt = torch.zeros(E, dtype=i32, device=dev).scatter_add_(0, flat, torch.ones_like(flat, dtype=i32))
-    pos = torch.empty(P, dtype=i32, device=dev)
-    pos[order] = torch.arange(P, dtype=i32, device=dev)
+    mk = lambda n: torch.empty(n, dtype=i32, device=dev)
+    pe, pt, pos, start, scratch = mk(P), mk(P), mk(P), mk(E + 2), mk(M.pf_sort_scratch_ints(P, E))
     plan = torch.empty(M.pf_plan_ints(E, P), dtype=i32, device=dev)
-    M.pf_plan(cnt, L.table, plan, P)
     status = torch.zeros(1, dtype=i32, device=dev)
     xg, xu = torch.empty(P, H, dtype=f16, device=dev), torch.empty(P, H, dtype=f16, device=dev)
     zg, zd = torch.zeros(P, 4, dtype=f32, device=dev), torch.zeros(P, 4, dtype=f32, device=dev)
     acc_g, acc_u = torch.empty(P, I, dtype=f32, device=dev), torch.empty(P, I, dtype=f32, device=dev)
     hbuf, y = torch.empty(P, I, dtype=f16, device=dev), torch.empty(P, H, dtype=f32, device=dev)
     out = torch.empty(T, H, dtype=f32, device=dev)
-    steps = [("pf_pre", lambda: M.pf_pre(x, pt, pe, L.table, xg, xu, zg, I, kperm=True)),
+    steps = [("pf_sort + plan", lambda: (M.pf_sort(sel, rw, L.table, pe, pt, pos, start, None, scratch), M.pf_plan_window(start, L.table, plan, 0, P))),
+             ("pf_pre", lambda: M.pf_pre(x, pt, pe, L.table, xg, xu, zg, I, kperm=True)),
              ("pf_gemm gate|up", lambda: M.pf_gemm(L.table, plan, xg, xu, acc_g, acc_u, H, I, L.nm_gu, L.nm_dn, False, status)),
              ("pf_mid", lambda: M.pf_mid(acc_g, acc_u, zg, pe, L.table, hbuf, zd, H, I, kperm=True)),
              ("pf_gemm down", lambda: M.pf_gemm(L.table, plan, hbuf, None, y, None, H, I, L.nm_gu, L.nm_dn, True, status)),
@@ -401,6 +397,7 @@ def layer_stack_case(cfg, rank, world, dev, n_layers=16, window=65536):
             if l == 0:
                 shared_peer = ep.peer
             ep.peer = shared_peer
+            ep.peer_decode = os.environ.get("NQ_EP_PEER_DECODE", "0") == "1"
             eps.append(ep)
     sel, rw = synth.routing(window, E, topk, SEED + 777)
     x = synth.tokens(window, H, SEED + 778)
@@ -459,9 +456,10 @@ def layer_stack_case(cfg, rank, world, dev, n_layers=16, window=65536):
 
     def decode_step(allreduce=True):
         for l in range(n_layers):
-            y = layers[l](x1, sel1, rw1)
             if world > 1 and allreduce:
-                dist.all_reduce(y)
+                eps[l].decode(x1, sel1, rw1)
+            else:
+                layers[l](x1, sel1, rw1)
 
     dt = {}
     for name, ar in (("step", True), ("kernels_only", False)):
@@ -538,6 +536,11 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t
 
+    epd = None
+    if world > 1:
+        from nestquant_b200.ep import EPLayer
+        epd = EPLayer(L, rank, world, peer_rows=64, peer_decode=os.environ.get("NQ_EP_PEER_DECODE", "0") == "1")
+
     def decode_case(B, steps, warmup, seed_off, want_kernel, want_e2e):
         """B tokens per step; returns dict(us_total, bytes_total, [k_us, k_bytes], [e2e_us], clocks)"""
         total = warmup + steps
@@ -552,10 +555,9 @@ def main():
         xd = [x.to(dev) for x in xs]
 
         def layer(i, x):
-            out = L(x, sels[i], rws[i])
             if world > 1:
-                dist.all_reduce(out)          # 24 KB per token: NCCL's all-reduce beats a barrier + peer-load kernel here
-            return out
+                return epd.decode(x, sels[i], rws[i])     # NCCL all-reduce of the partial outputs (NQ_EP_PEER_DECODE=1: barrier kernel + peer-load sum, measured slower: 155 vs 144 us on 2 GPUs)
+            return L(x, sels[i], rws[i])
 
         r = {}
         # device-resident timing: one event pair per step, L2 flushed (untimed) between steps
@@ -602,6 +604,8 @@ def main():
             b.record()
             barrier()
             r["allreduce_us"] = float(allmax(torch.tensor([a.elapsed_time(b) * 1e3 / 20], dtype=torch.float64, device=dev)))
+            r["sum_by"] = "barrier kernel + peer-load sum (nq_ep_barrier, nq_ep_combine)" if epd.peer is not None and epd.peer_decode else "NCCL all-reduce"
+            r["barrier_timed_out"] = bool(epd.peer is not None and epd.peer.timed_out())
         if want_e2e:
             # end to end through the public API from HOST buffers: host -> pinned -> device, layer, device -> host, all
             # inside one captured graph per call (what a serving engine does around this layer)
@@ -650,7 +654,7 @@ def main():
     r4 = decode_case(4, s4, 3, 50001, False, False)
 
     # prefill case (config 3): 8192 tokens, every resident expert at level 4, tokens sharded over the ranks
-    del L, experts
+    del L, experts, epd
     torch.cuda.empty_cache()
     from nestquant_b200.ep import EPLayer
     T_pf = 8192
@@ -712,7 +716,8 @@ def main():
                            "tokens_per_step": 1, "parallelism": f"ep{world}", "l2": "flushed between steps (256 MB write)"},
                 "layer_us": us_total / args.steps, "bytes_per_step": by_total / args.steps,
                 "decode_phases_us": {"kernel_gate_up_alone": r1["gu_us"], "kernel_down_alone": r1["dn_us"],
-                                     "allreduce_alone": r1.get("allreduce_us", 0.0),
+                                     "nccl_allreduce_alone": r1.get("allreduce_us", 0.0), "partial_outputs_summed_by": r1.get("sum_by", "one GPU: nothing to sum"),
+                                     "barrier_timed_out": r1.get("barrier_timed_out", False),
                                      "note": "this rank's kernel halves launched alone (each with the fixed cost of a launch), and NCCL's all-reduce of the [1, H] fp32 output back to back"},
                 "e2e": {"value": by_total / r1["e2e_us"] / 1e3, "unit": UNIT, "h2d_bytes_per_step": H * 2 + topk * 10,
                         "d2h_bytes_per_step": H * 4, "layer_us": r1["e2e_us"] / args.steps,

@@ -79,6 +79,18 @@ int nq_promote(void* slot, const void* host_record, size_t record_bytes, int64_t
  * Pairs = (token, expert) picks sorted by expert: pt[p] = token, pe[p] = expert, prw[p] = routing weight (fp16).
  * R = number of pairs in this call.  z arrays are fp32 [R][4] (low-rank inputs, rank <= 4). */
 
+/* The permutation of a prefill window: the T * topk picks sorted by expert with a stable counting sort on the device (three
+ * small kernels, no host sync).  Bin E collects the picks that contribute nothing - expert id outside [0, E), expert not
+ * resident (level <= 0), routing weight 0 - behind every real pair.
+ *   pe [P] expert (or E) and pt [P] token of sorted pair p;  pos [P]: sorted index of pick t * topk + k;
+ *   start [E + 2]: first pair of each bin (start[E] = number of live pairs, start[E + 1] = P);
+ *   hit_counts [E] or NULL: += picks with a valid id and a non-zero weight, whatever the level (caller zeroes it; feed it to
+ *   nq_pf_hits);  scratch: int32 [nq_pf_sort_scratch_ints(P, E)].
+ * Replaces the host side of the reference's prefill (sm120/moe.py:293-298: argsort, scatter_add, .cpu() of the counts). */
+int nq_pf_sort_scratch_ints(int pairs, int E);
+int nq_pf_sort(const int64_t* sel, const void* rw, const int64_t* table, int T, int topk, int E, int32_t* pe, int32_t* pt,
+               int32_t* pos, int32_t* start, int32_t* hit_counts, int32_t* scratch, int scratch_ints, void* stream);
+
 /* xg[p] = fp16(WHT128(x[pt[p]] * su_g)), xu[p] likewise with su_u, both [R][H]; zg[p][r] = x . V_gu[r].
  * Pairs of level-0 experts and pairs whose expert id is outside [0, E) (padding) are skipped (their rows are left untouched).
  * kperm != 0 writes xg / xu in the k order nq_pf_gemm reads: inside every 16 consecutive k, position 4 i + {0, 1}
@@ -124,8 +136,12 @@ int nq_pf_combine(const float* y, const float* zd, const int32_t* pos, const int
  *                out0 = y fp32 [pairs][H], act1 / out1 unused).  The activation matrices must be in the k order
  *                nq_pf_pre / nq_pf_mid write with kperm = 1.  Rows of pairs whose expert is not resident are not
  *                written.  status: int32 [1] on the device, set to 1 if a device-side wait timed out (bounded waits;
- *                the outputs are then invalid) - read it after synchronising. */
+ *                the outputs are then invalid) - read it after synchronising.
+ *   nq_pf_plan_window   the same from nq_pf_sort's start array for the pairs [pair0, pair0 + npairs) of the sorted list
+ *                (rows counted from pair0): the pass list of one scratch chunk. */
 int nq_pf_plan_ints(int E, int pairs);
+int nq_pf_plan_window(const int32_t* start, const int64_t* table, int E, int pair0, int npairs, int32_t* plan, int plan_ints,
+                      void* stream);
 int nq_pf_plan(const int32_t* counts, const int64_t* table, int E, int pairs, int32_t* plan, int plan_ints, void* stream);
 int nq_pf_gemm(const int64_t* table, const int32_t* plan, const void* act0, const void* act1, int pairs, float* out0, float* out1,
                int H, int I, int nm_gu, int nm_dn, int down, int32_t* status, void* stream);

@@ -61,6 +61,9 @@ SIGNATURES = {
     "nq_pf_post": (_i, [_p, _p, _p, _p, _p, _i, _p, _i, _p, _i, _i, _p]),
     "nq_pf_combine": (_i, [_p, _p, _p, _p, _p, _i, _i, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
     "nq_pf_hits": (_i, [_p, _p, _i, _p]),
+    "nq_pf_sort_scratch_ints": (_i, [_i, _i]),
+    "nq_pf_sort": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i, _p]),
+    "nq_pf_plan_window": (_i, [_p, _p, _i, _i, _i, _p, _i, _p]),
     "nq_pf_plan_ints": (_i, [_i, _i]),
     "nq_pf_plan": (_i, [_p, _p, _i, _i, _p, _i, _p]),
     "nq_pf_gemm": (_i, [_p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p]),

@@ -519,6 +519,27 @@ __global__ void pf_plan_kernel(const int* __restrict__ counts, const int64_t* __
     plan[0] = n; plan[1] = covered; plan[2] = plan[3] = 0;
 }
 
+// The same from the sorted pair list of a whole window: start[e] = first pair of expert e (start[E] = end of the last
+// expert's pairs); the plan covers the pairs [pair0, pair0 + npairs) with rows counted from pair0.
+__global__ void pf_plan_window_kernel(const int* __restrict__ start, const int64_t* __restrict__ table, int E, int pair0, int npairs,
+                                      int* plan, int max_passes)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    PfPass* out = (PfPass*)(plan + 4);
+    int n = 0, covered = 0;
+    for (int e = 0; e < E; ++e)
+    {
+        const int a = max(start[e], pair0), b = min(start[e + 1], pair0 + npairs), c = b - a;
+        if (c > 0 && table[(int64_t)e * kTableWidth] > 0)
+            for (int t0 = 0; t0 < c && n < max_passes; t0 += kPfTokens)
+            {
+                out[n].expert = e; out[n].row0 = a - pair0 + t0; out[n].ntok = c - t0 < kPfTokens ? c - t0 : kPfTokens; out[n].pad = 0;
+                covered += out[n].ntok; ++n;
+            }
+    }
+    plan[0] = n; plan[1] = covered; plan[2] = plan[3] = 0;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -556,6 +577,14 @@ int nq_pf_plan(const int32_t* counts, const int64_t* table, int E, int pairs, in
     NQ_REQUIRE(plan_ints >= nq_pf_plan_ints(E, pairs), "nq_pf_plan: plan needs %d ints", nq_pf_plan_ints(E, pairs));
     nq::pf_plan_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counts, table, E, plan, (plan_ints - 4) / 4);
     return nq::check_launch("nq_pf_plan");
+}
+
+int nq_pf_plan_window(const int32_t* start, const int64_t* table, int E, int pair0, int npairs, int32_t* plan, int plan_ints, void* stream)
+{
+    NQ_REQUIRE(start && table && plan && E > 0 && pair0 >= 0 && npairs >= 0, "nq_pf_plan_window: bad arguments");
+    NQ_REQUIRE(plan_ints >= nq_pf_plan_ints(E, npairs), "nq_pf_plan_window: plan needs %d ints", nq_pf_plan_ints(E, npairs));
+    nq::pf_plan_window_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(start, table, E, pair0, npairs, plan, (plan_ints - 4) / 4);
+    return nq::check_launch("nq_pf_plan_window");
 }
 
 int nq_pf_gemm(const int64_t* table, const int32_t* plan, const void* act0, const void* act1, int pairs, float* out0, float* out1,

@@ -109,6 +109,31 @@ def pf_combine(y, zd, pos, sel, rw, table, out, I, pair0=0, npairs=None, accumul
                               pair0, npairs, int(bool(accumulate)), current_stream()), "pf_combine")
 
 
+def pf_sort_scratch_ints(pairs, E):
+    return int(lib().nq_pf_sort_scratch_ints(pairs, E))
+
+
+def pf_sort(sel, rw, table, pe, pt, pos, start, hit_counts, scratch):
+    """the (token, pick) pairs sorted by expert on the device (stable counting sort, no host sync): pe / pt int32 [T*topk]
+    expert (E = contributes nothing) and token of each sorted pair, pos int32 [T*topk] sorted index of each pick, start int32
+    [E+2] first pair of each bin; hit_counts int32 [E] (zeroed by the caller) or None; scratch int32 [pf_sort_scratch_ints]"""
+    _need(sel, torch.int64, "sel"); _need(rw, torch.float16, "rw"); _need(table, torch.int64, "table")
+    for t, n in ((pe, "pe"), (pt, "pt"), (pos, "pos"), (start, "start"), (scratch, "scratch")):
+        _need(t, torch.int32, n)
+    T, topk = sel.shape
+    E, P = table.shape[0], T * topk
+    if rw.numel() < P or pe.numel() < P or pt.numel() < P or pos.numel() < P or start.numel() < E + 2 or (hit_counts is not None and hit_counts.numel() < E):
+        raise NestQuantError("pf_sort sizes")
+    check(lib().nq_pf_sort(ptr(sel), ptr(rw), ptr(table), T, topk, E, ptr(pe), ptr(pt), ptr(pos), ptr(start), ptr(hit_counts), ptr(scratch),
+                           scratch.numel(), current_stream()), "pf_sort")
+
+
+def pf_plan_window(start, table, plan, pair0, npairs):
+    """pass list of the fused prefill GEMM for the pairs [pair0, pair0 + npairs) of a sorted window (start from pf_sort)"""
+    _need(start, torch.int32, "start"); _need(table, torch.int64, "table"); _need(plan, torch.int32, "plan")
+    check(lib().nq_pf_plan_window(ptr(start), ptr(table), table.shape[0], pair0, npairs, ptr(plan), plan.numel(), current_stream()), "pf_plan_window")
+
+
 def pf_plan_ints(E, pairs):
     return int(lib().nq_pf_plan_ints(E, pairs))
 

@@ -390,33 +390,24 @@ class MoELayer:
         tb = s.table if table is None else table
         P = T * k
         R = max(1, min(R or 65536, P))
-        i32 = torch.int32
         out = torch.empty(T, H, dtype=torch.float32, device=dev) if out is None else out
         if P == 0:
             return out
         sc = s._prefill_scratch(R, dev)
-        flat, rwf = sel.reshape(-1), rw.reshape(-1)
-        # bin E collects the picks that contribute nothing: no valid expert id, expert not resident here, zero weight.  They
-        # sort behind every real pair and get no pass; the kernels skip their rows.
-        live = (flat >= 0) & (flat < E) & (rwf != 0)
-        live &= tb[flat.clamp(0, E - 1), 0] > 0
-        key = torch.where(live, flat, E)
-        order = torch.argsort(key, stable=True)
-        pe, pt = key[order].to(i32), (order // k).to(i32)
-        one = torch.ones_like(key, dtype=i32)
-        cnt = torch.zeros(E + 1, dtype=i32, device=dev).scatter_add_(0, key, one)
-        pos = torch.empty(P, dtype=i32, device=dev)
-        pos[order] = torch.arange(P, dtype=i32, device=dev)
+        # pairs sorted by expert on the device: pe / pt of each sorted pair, pos of each pick, first pair of each expert.  Picks
+        # that contribute nothing (no valid expert id, expert not resident here, zero weight) sort behind every real pair.
+        sel, rw = sel.contiguous(), rw.contiguous()
+        perm = s._prefill_perm(P, dev)
+        pe, pt, pos = perm["pe"][:P], perm["pt"][:P], perm["pos"][:P]
+        hit = None
         if s.hits_ptr:
-            hit = torch.where((flat >= 0) & (flat < E) & (rwf != 0), flat, E)      # every pick with a weight, whatever the level
-            M.pf_hits(torch.zeros(E + 1, dtype=i32, device=dev).scatter_add_(0, hit, one)[:E].contiguous(), s.hits_ptr)
-        end = torch.cumsum(cnt, 0, dtype=i32)
-        start = end - cnt
+            hit = perm["hit"].zero_()
+        M.pf_sort(sel, rw, tb, pe, pt, pos, perm["start"], hit, perm["scratch"])
+        if s.hits_ptr:
+            M.pf_hits(hit, s.hits_ptr)
         for c0 in range(0, P, R):
             n = min(R, P - c0)
-            # pairs of each expert inside this chunk -> pass list (built on the device, no host sync)
-            cnt_c = (torch.clamp(end, max=c0 + n) - torch.clamp(start, min=c0)).clamp_(min=0)[:E].contiguous()
-            M.pf_plan(cnt_c, tb, sc["plan"], n)
+            M.pf_plan_window(perm["start"], tb, sc["plan"], c0, n)       # pass list of this chunk, built on the device
             xg, xu, y = sc["xg"][:n], sc["xu"][:n], sc["y"][:n]
             if x_peers is None:
                 M.pf_pre(x, pt[c0:c0 + n], pe[c0:c0 + n], tb, xg, xu, sc["zg"], I, kperm=True)
@@ -449,6 +440,19 @@ class MoELayer:
                         zd=torch.zeros(R, 4, dtype=f32, device=dev),
                         plan=torch.empty(s.M.pf_plan_ints(E, R), dtype=i32, device=dev), status=status)
         return s._pf_sc
+
+    def _prefill_perm(s, P, dev):
+        """index arrays of the pair sort for windows of up to P pairs, kept between calls"""
+        owner = getattr(s, "_pf_owner", None)
+        if owner is not None:
+            return owner._prefill_perm(P, dev)
+        pm = getattr(s, "_pf_perm", None)
+        if pm is not None and pm["P"] >= P and pm["pe"].device == dev:
+            return pm
+        i32 = torch.int32
+        mk = lambda n: torch.empty(n, dtype=i32, device=dev)
+        s._pf_perm = dict(P=P, pe=mk(P), pt=mk(P), pos=mk(P), start=mk(s.E + 2), hit=mk(s.E), scratch=mk(max(1, s.M.pf_sort_scratch_ints(P, s.E))))
+        return s._pf_perm
 
     def share_prefill_scratch(s, other):
         """use the prefill scratch (and status word) of another layer of the same shape: the layers of a stack run one after

@@ -176,3 +176,38 @@ def test_pf_helpers_reject_bad_sizes():
         ext.pf_pre(x, idx, idx, t, x, x, torch.zeros(3, 4, device="cuda"), 128)       # xg too small for 3 pairs
     with pytest.raises(NestQuantError):
         ext.pf_pre(x.float(), idx, idx, t, x, x, torch.zeros(3, 4, device="cuda"), 128)
+
+
+def test_pair_sort_is_a_stable_counting_sort():
+    """nq_pf_sort against torch's stable argsort of the same keys: live picks by expert in pick order, then everything that
+    contributes nothing (padding ids, experts that are not resident, zero weights); hit counts as the reference counts them"""
+    from nestquant_b200 import ext, moe
+    H, I, NE, topk, T = 256, 128, 37, 5, 1111           # 5555 picks: 22 slices, the last one ragged
+    exs = [moe.Expert(H, I, seed=i, sv=0.02) for i in range(3)]
+    L = moe.MoELayer(NE, H, I, Bmax=1, topk=topk)
+    for e in range(NE):
+        L.set(e, exs[e % 3], 0 if e % 7 == 3 else 2)
+    g = torch.Generator().manual_seed(3)
+    sel = torch.randint(-2, NE + 2, (T, topk), generator=g)
+    rw = torch.rand(T, topk, generator=g).half()
+    rw[torch.rand(T, topk, generator=g) < 0.1] = 0
+    P = T * topk
+    mk = lambda n: torch.empty(n, dtype=torch.int32, device="cuda")
+    pe, pt, pos, start = mk(P), mk(P), mk(P), mk(NE + 2)
+    hits = torch.zeros(NE, dtype=torch.int32, device="cuda")
+    ext.pf_sort(sel.cuda(), rw.cuda(), L.table, pe, pt, pos, start, hits, mk(ext.pf_sort_scratch_ints(P, NE)))
+    torch.cuda.synchronize()
+    flat, rwf = sel.reshape(-1), rw.reshape(-1)
+    valid = (flat >= 0) & (flat < NE) & (rwf != 0)
+    level = L.table[:, 0].cpu()
+    live = valid & (level[flat.clamp(0, NE - 1)] > 0)
+    key = torch.where(live, flat, NE)
+    order = torch.argsort(key, stable=True)
+    assert torch.equal(pe.cpu().long(), key[order]) and torch.equal(pt.cpu().long(), order // topk)
+    inv = torch.empty(P, dtype=torch.long)
+    inv[order] = torch.arange(P)
+    assert torch.equal(pos.cpu().long(), inv)
+    want_start = torch.zeros(NE + 2, dtype=torch.long)
+    want_start[1:] = torch.cumsum(torch.bincount(key, minlength=NE + 1), 0)
+    assert torch.equal(start.cpu().long(), want_start)
+    assert torch.equal(hits.cpu().long(), torch.bincount(flat[valid], minlength=NE))
