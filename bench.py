@@ -398,6 +398,7 @@ def layer_stack_case(cfg, rank, world, dev, n_layers=16, window=65536):
                 shared_peer = ep.peer
             ep.peer = shared_peer
             ep.peer_decode = os.environ.get("NQ_EP_PEER_DECODE", "0") == "1"
+            ep.fused_decode = os.environ.get("NQ_EP_FUSED_DECODE", "1") != "0"
             eps.append(ep)
     sel, rw = synth.routing(window, E, topk, SEED + 777)
     x = synth.tokens(window, H, SEED + 778)
@@ -539,7 +540,10 @@ def main():
     epd = None
     if world > 1:
         from nestquant_b200.ep import EPLayer
-        epd = EPLayer(L, rank, world, peer_rows=64, peer_decode=os.environ.get("NQ_EP_PEER_DECODE", "0") == "1")
+        # partial outputs summed inside the layer kernel over peer memory; NQ_EP_FUSED_DECODE=0: NCCL all-reduce after the kernel
+        # (or, with NQ_EP_PEER_DECODE=1, a barrier kernel + a sum kernel)
+        epd = EPLayer(L, rank, world, peer_rows=64, peer_decode=os.environ.get("NQ_EP_PEER_DECODE", "0") == "1",
+                      fused_decode=os.environ.get("NQ_EP_FUSED_DECODE", "1") != "0")
 
     def decode_case(B, steps, warmup, seed_off, want_kernel, want_e2e):
         """B tokens per step; returns dict(us_total, bytes_total, [k_us, k_bytes], [e2e_us], clocks)"""
@@ -556,7 +560,7 @@ def main():
 
         def layer(i, x):
             if world > 1:
-                return epd.decode(x, sels[i], rws[i])     # NCCL all-reduce of the partial outputs (NQ_EP_PEER_DECODE=1: barrier kernel + peer-load sum, measured slower: 155 vs 144 us on 2 GPUs)
+                return epd.decode(x, sels[i], rws[i])
             return L(x, sels[i], rws[i])
 
         r = {}
@@ -604,19 +608,21 @@ def main():
             b.record()
             barrier()
             r["allreduce_us"] = float(allmax(torch.tensor([a.elapsed_time(b) * 1e3 / 20], dtype=torch.float64, device=dev)))
-            r["sum_by"] = "barrier kernel + peer-load sum (nq_ep_barrier, nq_ep_combine)" if epd.peer is not None and epd.peer_decode else "NCCL all-reduce"
+            r["sum_by"] = ("the layer kernel itself (peer stores + per-group arrival counters, nq_moe_forward_ep)" if epd.peer is not None and epd.fused_decode
+                           else "barrier kernel + peer-load sum (nq_ep_barrier, nq_ep_combine)" if epd.peer is not None and epd.peer_decode else "NCCL all-reduce")
             r["barrier_timed_out"] = bool(epd.peer is not None and epd.peer.timed_out())
         if want_e2e:
             # end to end through the public API from HOST buffers: host -> pinned -> device, layer, device -> host, all
             # inside one captured graph per call (what a serving engine does around this layer)
-            G = L.capture(B, host_io=True)
+            fused = world > 1 and epd.peer is not None and epd.fused_decode
+            G = L.capture(B, host_io=True, ep=epd.ep_args() if fused else None)
             e2 = []
             for i in range(total):
                 flush.zero_(); torch.cuda.synchronize()
                 t0 = time.perf_counter()
                 G.x_host.copy_(xs[i]); G.sel_host.copy_(sel_h[i]); G.rw_host.copy_(rw_h[i])
                 G.replay()
-                if world > 1:
+                if world > 1 and not fused:
                     dist.all_reduce(G.out)
                     G.out_host.copy_(G.out, non_blocking=True)
                 torch.cuda.synchronize()

@@ -206,6 +206,25 @@ typedef struct NqMoeForward {
 
 int nq_moe_forward(const NqMoeForward* args, void* stream);
 
+/* The same layer call on one rank of an expert-parallel group, with the all-reduce of the partial outputs done inside the
+ * kernel over peer memory: every rank calls it with the same tokens and picks and a table that marks the other ranks'
+ * experts level 0; out receives the sum over all ranks, bitwise equal on every rank (slices are added in rank order).
+ * peer_recv[r] / peer_counters[r]: device addresses, as seen from this GPU, of rank r's receive buffer (fp32
+ * [nq_moe_ep_recv_floats(world, H)]) and arrival counters (int32 [nq_moe_ep_counter_ints()], zero before the first call);
+ * symmetric memory or peer mappings over NVLink.  epoch: device int32, zero before the first call, private to this rank.
+ * Plain peer stores, one remote atomic add per (token, 128-column group) and peer, bounded waits (2 s, then cnt_h[0] = 1).
+ * All ranks must make the same sequence of calls with these buffers; which must be 3.  No counterpart in the reference (its
+ * evaluation harness all-reduces with the collective library, sm120/eval/eval_reg.py:137-142,181). */
+typedef struct NqMoeEp {
+    int world, rank;
+    void* const* peer_recv;
+    int32_t* const* peer_counters;
+    int32_t* epoch;
+} NqMoeEp;
+size_t nq_moe_ep_recv_floats(int world, int H);
+size_t nq_moe_ep_counter_ints(void);
+int nq_moe_forward_ep(const NqMoeForward* args, const NqMoeEp* ep, void* stream);
+
 /* The same layer call for hosts that must not allocate - a plugin inside a serving engine that has already handed all
  * device memory to its caches, or a process that bans allocator calls on its hot thread.  No counterpart in the reference
  * (its workspaces are always torch tensors owned by the caller).  The workspaces of nq_moe_forward live in an array that

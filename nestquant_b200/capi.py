@@ -32,6 +32,10 @@ class NqMoeForward(C.Structure):
                                    "which")])
 
 
+class NqMoeEp(C.Structure):
+    _fields_ = [("world", _i), ("rank", _i), ("peer_recv", C.POINTER(_p)), ("peer_counters", C.POINTER(_p)), ("epoch", _p)]
+
+
 class NqEngineDone(C.Structure):
     _fields_ = [("tag", _i64), ("hit", C.c_int32), ("t_read_s", C.c_double), ("t_done_s", C.c_double)]
 
@@ -69,6 +73,9 @@ SIGNATURES = {
     "nq_pf_gemm": (_i, [_p, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p]),
     "nq_moe_workspace": (_i, [_i, _i, _i, _i, _i, _i, C.POINTER(NqMoeWorkspace)]),
     "nq_moe_forward": (_i, [C.POINTER(NqMoeForward), _p]),
+    "nq_moe_forward_ep": (_i, [C.POINTER(NqMoeForward), C.POINTER(NqMoeEp), _p]),
+    "nq_moe_ep_recv_floats": (_sz, [_i, _i]),
+    "nq_moe_ep_counter_ints": (_sz, []),
     "nq_moe_static_scratch_bytes": (_sz, []),
     "nq_moe_forward_static": (_i, [_p, _p, _p, _p, _p] + [_i] * 9 + [_p, _p]),
     "nq_salience": (_i, [_p, _i, _i64, _p, _p, _i, _i, _i, _i, C.c_float, _p, _p, _p]),

@@ -53,6 +53,7 @@ constexpr int kRunTiles = 4;     // column tiles (8 tokens each) of mma.m16n8k16
 constexpr int kRunTokens = 8 * kRunTiles;
 constexpr int kRotBlocks = 4;    // 128-blocks per rotation piece
 constexpr unsigned long long kWaitNs = 2000000000ull;
+constexpr int kEpRanks = 8, kEpTokens = NQ_MAX_TOKENS, kEpGroups = 64;   // limits of the in-kernel all-reduce
 
 struct RunRec { int expert, level, first, count; };   // picks of the run: order[first .. first + count)
 
@@ -68,10 +69,15 @@ struct MoeArgs
     float* part_d;     // [ks_dn][S][H]
     int* cnt_gu;       // [S * I/128] (run, group) arrivals, [S * I/128] (run, 512-block) arrivals, [S] finished groups per run
     int* cnt_d;        // [B][H/128] (token, group) arrivals
-    int* wq;           // [0] piece queue, [1] CTAs that left, [2] finished rotation pieces
+    int* wq;           // [0] piece queue, [1] CTAs that left, [2] finished rotation pieces, [3] queue of the all-reduce tasks
     float* zd;         // [S][I/128][4] down low-rank partials
     float* out;        // [B][H]
     int* hits;         // optional [E] pick counters (may be host-mapped)
+    // expert parallelism (world > 1): the all-reduce of the partial outputs runs inside this kernel, over peer memory
+    int world, rank;
+    float* recv[kEpRanks];   // every rank's receive buffer [2][world][32][H] fp32, as seen from this GPU
+    int* rcnt[kEpRanks];     // every rank's arrival counters [2][32 * 64], as seen from this GPU
+    int* epoch;              // this rank's call counter (device): its parity picks the half of recv / rcnt
 };
 
 __device__ __forceinline__ bool pick_valid(const MoeArgs& a, int s, int* expert, int* level)
@@ -542,8 +548,57 @@ __device__ __forceinline__ void finish_gate_up(const MoeArgs& a, const Shape& sh
     }
 }
 
+// ---- all-reduce of the partial outputs inside the kernel (expert parallelism) --------------------------------------------
+// Every rank computes, for each (token, 128-column group), the weighted sum over ITS experts.  It stores that slice into
+// slot [parity][its rank][token] of every rank's receive buffer (plain peer stores over NVLink, its own buffer included),
+// then adds 1 to the (token, group) arrival counter of every rank (release, system scope).  After its own pieces are done, a
+// rank's warps take (token, group) tasks: wait until the counter shows all `world` slices (acquire; bounded), add the slices
+// in rank order - every rank gets bitwise the same sums - and write out.  The parity of a per-rank call counter alternates
+// two halves of the buffers: a rank can run at most one call ahead of a peer (it needs the peer's slices of call n to finish
+// call n), so the slices of call n + 1 never land on slices of call n that are still being read.
+__device__ __forceinline__ void ep_send(const MoeArgs& a, const Shape& sh, int par, int b, int grp, int lane, const float (&o)[4])
+{
+    const size_t at = (((size_t)par * a.world + a.rank) * kEpTokens + b) * a.H + grp * 128 + lane * 4;
+    for (int p = 0; p < a.world; ++p) *(float4*)(a.recv[p] + at) = make_float4(o[0], o[1], o[2], o[3]);
+    __threadfence_system();
+    __syncwarp();
+    if (lane < a.world)
+        asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(a.rcnt[lane] + (par * kEpTokens + b) * kEpGroups + grp) : "memory");
+}
+// false = the wait ran out
+__device__ __forceinline__ bool ep_sum(const MoeArgs& a, const Shape& sh, int par, int b, int grp, int lane)
+{
+    int* cnt = a.rcnt[a.rank] + (par * kEpTokens + b) * kEpGroups + grp;
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i)
+    {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+        if (v >= a.world) break;
+        if ((i & 31u) == 31u)
+        {
+            if (ld_acquire(a.status) != 0) return false;
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > kWaitNs) { atomicExch(a.status, 1); return false; }
+        }
+        __nanosleep(100);
+    }
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < a.world; ++p)
+    {
+        const float4 v = __ldcg((const float4*)(a.recv[a.rank] + (((size_t)par * a.world + p) * kEpTokens + b) * a.H + grp * 128 + lane * 4));
+        o[0] += v.x; o[1] += v.y; o[2] += v.z; o[3] += v.w;
+    }
+    *(float4*)(a.out + (size_t)b * a.H + grp * 128 + lane * 4) = make_float4(o[0], o[1], o[2], o[3]);
+    __syncwarp();
+    if (lane == 0) *cnt = 0;          // this half is next used two calls from now
+    return true;
+}
+
 // output rows [grp * 128, +128) of token b are complete in every k-slice of every pick: weighted combine
-__device__ __forceinline__ void finish_down(const MoeArgs& a, const Shape& sh, const Route& R, int b, int grp, int lane)
+__device__ __forceinline__ void finish_down(const MoeArgs& a, const Shape& sh, const Route& R, int b, int grp, int lane, int par)
 {
     __syncwarp();        // the acquiring arrival (some lane's) is ordered before every lane's loads below
     const int S = sh.S, N = a.H, KS = sh.KSd, col = grp * 128 + lane * 4;
@@ -587,7 +642,8 @@ __device__ __forceinline__ void finish_down(const MoeArgs& a, const Shape& sh, c
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[i] += w * v[i];
     }
-    *(float4*)(a.out + (size_t)b * a.H + col) = make_float4(o[0], o[1], o[2], o[3]);
+    if (a.world > 1) ep_send(a, sh, par, b, grp, lane, o);
+    else *(float4*)(a.out + (size_t)b * a.H + col) = make_float4(o[0], o[1], o[2], o[3]);
 }
 
 // ---------------------------------------------------------------- GEMV pieces
@@ -662,11 +718,25 @@ __global__ void __launch_bounds__(kThreads, NQ_GEMV_MINBLOCKS) moe_decode_kernel
         const int64_t es = a.sel[threadIdx.x];
         if (es >= 0 && es < a.E && __half2float(a.rw[threadIdx.x]) != 0.f) atomicAdd(a.hits + es, 1);   // every pick with a weight, any level
     }
-    // rows of tokens none of whose picks is resident are defined as zero (nothing else writes them)
+    const bool ep = a.world > 1 && a.which == 3;
+    const int par = ep ? (*(volatile int*)a.epoch & 1) : 0;
+    // rows of tokens none of whose picks is resident here are defined as zero (nothing else writes them); under expert
+    // parallelism this rank's slice of such a token is a zero slice, sent like any other
     if (a.which & 2)
-        for (int b = blockIdx.x; b < a.B; b += gridDim.x)
-            if (R.nvalid[b] == 0)
-                for (int i = threadIdx.x; i < a.H; i += kThreads) a.out[(size_t)b * a.H + i] = 0.f;
+    {
+        if (!ep)
+        {
+            for (int b = blockIdx.x; b < a.B; b += gridDim.x)
+                if (R.nvalid[b] == 0)
+                    for (int i = threadIdx.x; i < a.H; i += kThreads) a.out[(size_t)b * a.H + i] = 0.f;
+        }
+        else
+        {
+            const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int task = (int)blockIdx.x * kWarps + warp; task < a.B * sh.ngH; task += (int)gridDim.x * kWarps)
+                if (R.nvalid[task / sh.ngH] == 0) ep_send(a, sh, par, task / sh.ngH, task % sh.ngH, lane, zero);
+        }
+    }
 
     const uint32_t ring = smem_addr(smem_ring) + warp * (kDepth * kGemvStage);
     const int total = sh.n_rot + sh.n_gu + sh.n_dn;
@@ -739,10 +809,20 @@ __global__ void __launch_bounds__(kThreads, NQ_GEMV_MINBLOCKS) moe_decode_kernel
             {
                 const int src = __ffs(todo) - 1;
                 todo &= todo - 1;
-                finish_down(a, sh, R, __shfl_sync(0xffffffffu, b, src), grp, lane);
+                finish_down(a, sh, R, __shfl_sync(0xffffffffu, b, src), grp, lane, par);
             }
         }
     }
+    // this rank's pieces are done (or handed out): add up the slices of all ranks, one (token, group) at a time
+    if (ep)
+        for (;;)
+        {
+            int task = 0;
+            if (lane == 0) task = atomicAdd(a.wq + 3, 1);
+            task = __shfl_sync(0xffffffffu, task, 0);
+            if (task >= a.B * sh.ngH) break;
+            if (!ep_sum(a, sh, par, task / sh.ngH, task % sh.ngH, lane)) break;
+        }
     // the last CTA to leave resets the queue and the per-run counters (graph replays start from zero)
     __syncthreads();
     if (threadIdx.x == 0)
@@ -750,7 +830,8 @@ __global__ void __launch_bounds__(kThreads, NQ_GEMV_MINBLOCKS) moe_decode_kernel
         __threadfence();
         if (atomicAdd(a.wq + 1, 1) == (int)gridDim.x - 1)
         {
-            a.wq[0] = 0; a.wq[1] = 0; a.wq[2] = 0;
+            a.wq[0] = 0; a.wq[1] = 0; a.wq[2] = 0; a.wq[3] = 0;
+            if (ep) *a.epoch = *(volatile int*)a.epoch + 1;
             for (int r = 0; r < sh.nruns; ++r) a.cnt_gu[2 * sh.S * sh.ng + r] = 0;
             if (ld_acquire(a.status) != 0)      // a wait ran out: leave every counter clean all the same
             {
@@ -802,7 +883,7 @@ int nq_moe_workspace(int B, int topk, int H, int I, int ks_gu, int ks_dn, NqMoeW
     return NQ_OK;
 }
 
-int nq_moe_forward(const NqMoeForward* p, void* stream)
+static int moe_forward(const NqMoeForward* p, const NqMoeEp* ep, void* stream)
 {
     NQ_REQUIRE(p, "nq_moe_forward: null arguments");
     NQ_REQUIRE(p->G == 4, "nq_moe_forward: ring width G = %d (only 4 is built)", p->G);
@@ -827,6 +908,20 @@ int nq_moe_forward(const NqMoeForward* p, void* stream)
     a.force_level = p->force_level; a.ks_gu = p->ks_gu; a.ks_dn = p->ks_dn; a.which = p->which & 3; a.table = p->table;
     a.status = p->cnt_h; a.h = (__half*)p->h; a.xrot = a.h + (size_t)p->B * p->topk * p->I;
     a.part_gu = p->acc_gu; a.part_d = p->acc_d; a.zd = p->zd; a.cnt_gu = p->cnt_gu; a.cnt_d = p->cnt_d; a.wq = p->wq; a.out = p->out; a.hits = p->hits;
+    a.world = 1; a.rank = 0;
+    if (ep && ep->world > 1)
+    {
+        NQ_REQUIRE(ep->world <= nq::kEpRanks && ep->rank >= 0 && ep->rank < ep->world, "nq_moe_forward_ep: rank %d of %d", ep->rank, ep->world);
+        NQ_REQUIRE(ep->peer_recv && ep->peer_counters && ep->epoch, "nq_moe_forward_ep: null exchange buffers");
+        NQ_REQUIRE((p->which & 3) == 3, "nq_moe_forward_ep: the in-kernel all-reduce needs the whole layer call (which = 3)");
+        NQ_REQUIRE(p->H / 128 <= nq::kEpGroups && p->B <= nq::kEpTokens, "nq_moe_forward_ep: shape beyond the exchange buffers");
+        a.world = ep->world; a.rank = ep->rank; a.epoch = ep->epoch;
+        for (int r = 0; r < ep->world; ++r)
+        {
+            NQ_REQUIRE(ep->peer_recv[r] && ep->peer_counters[r] && nq::aligned16(ep->peer_recv[r]), "nq_moe_forward_ep: buffers of rank %d are null or misaligned", r);
+            a.recv[r] = (float*)ep->peer_recv[r]; a.rcnt[r] = (int*)ep->peer_counters[r];
+        }
+    }
     const int ctas = nq::resident_ctas();
     if (ctas <= 0) return nq::fail(NQ_ERR_CUDA, "nq_moe_forward: cannot reserve %d bytes of shared memory", nq::kGemvSmem);
     cudaLaunchConfig_t cfg = {};
@@ -839,5 +934,16 @@ int nq_moe_forward(const NqMoeForward* p, void* stream)
     if (e != cudaSuccess) return nq::fail(NQ_ERR_CUDA, "nq_moe_forward: %s", cudaGetErrorString(e));
     return nq::check_launch("nq_moe_forward");
 }
+
+int nq_moe_forward(const NqMoeForward* p, void* stream) { return moe_forward(p, nullptr, stream); }
+
+int nq_moe_forward_ep(const NqMoeForward* p, const NqMoeEp* ep, void* stream)
+{
+    NQ_REQUIRE(ep, "nq_moe_forward_ep: null exchange description");
+    return moe_forward(p, ep, stream);
+}
+
+size_t nq_moe_ep_recv_floats(int world, int H) { return world >= 1 && H > 0 ? (size_t)2 * world * nq::kEpTokens * H : 0; }
+size_t nq_moe_ep_counter_ints(void) { return (size_t)2 * nq::kEpTokens * nq::kEpGroups; }
 
 }  // extern "C"

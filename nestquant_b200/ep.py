@@ -66,7 +66,8 @@ class PeerBuffers:
 
     part   fp32 [rows, H]      partial output rows of the prefill (row = global token)
     xbuf   fp16 [rows_x, H]    this rank's input rows, read by the peers' first prefill pass
-    dec    2 x fp32 [32, H]    partial outputs of the decode path (alternating)
+    dec    2 x fp32 [32, H]    partial outputs of the decode path (alternating), for the barrier + sum-kernel variant
+    recv   fp32 [2, world, 32, H], rcnt int32 [2, 32 * 64]   receive slots and arrival counters of the in-kernel all-reduce
     flags  int32 [8]           barrier flags: flag [r] = last call number rank r announced to this rank
 
     torch's symmetric-memory module only allocates and exchanges the addresses; the barrier is nq_ep_barrier, whose wait is
@@ -89,6 +90,12 @@ class PeerBuffers:
         for _ in range(2):
             b, p = shared(32, H, dtype=torch.float32)
             s.dec.append(b); s.dec_ptrs.append(p)
+        from .capi import lib
+        # in-kernel all-reduce of the decode path: receive slots and arrival counters of every rank, this rank's call counter
+        s.recv, s.recv_ptrs = shared(int(lib().nq_moe_ep_recv_floats(world, H)), dtype=torch.float32)
+        s.rcnt, s.rcnt_ptrs = shared(int(lib().nq_moe_ep_counter_ints()), dtype=torch.int32)
+        s.rcnt.zero_()
+        s.dec_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         s.flags, s.flag_ptrs = shared(8, dtype=torch.int32)
         s.flags.zero_()
         s.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -109,9 +116,11 @@ class PeerBuffers:
 
 
 class EPLayer:
-    def __init__(s, local_layer, rank=None, world=None, group=None, peer_rows=0, peer_decode=False, timeout_s=2.0):
+    def __init__(s, local_layer, rank=None, world=None, group=None, peer_rows=0, peer_decode=False, timeout_s=2.0, fused_decode=True):
         """peer_rows > 0: exchange over peer memory for up to that many tokens of the whole group per prefill call (NCCL groups
-        on peer-connected GPUs only; silently off where symmetric memory cannot be set up)."""
+        on peer-connected GPUs only; silently off where symmetric memory cannot be set up).  With peer buffers, decode() sums
+        the ranks' partial outputs inside the layer kernel (fused_decode), or by a barrier kernel + sum kernel (peer_decode),
+        or, without either, by the collective library's all-reduce."""
         s.L, s.group = local_layer, group
         s.rank = dist.get_rank(group) if rank is None else rank
         s.world = dist.get_world_size(group) if world is None else world
@@ -119,7 +128,7 @@ class EPLayer:
         s.per = (s.E + s.world - 1) // s.world
         s.last_stats = {}
         s.peer = None
-        s.peer_decode = peer_decode
+        s.peer_decode, s.fused_decode = peer_decode, fused_decode
         s.events = None              # set to [] to have prefill() record (label, cuda event) marks between its phases
         s._same = set()
         if peer_rows > 0 and s.world > 1 and s.world <= 8 and _has_alltoall(group):
@@ -134,6 +143,11 @@ class EPLayer:
             if int(ok) == 0:
                 s.peer = None
 
+    def ep_args(s):
+        """the `ep` argument of MoELayer.__call__ / .capture for this rank, or None without peer buffers"""
+        P = s.peer
+        return None if P is None or s.world == 1 else (s.world, s.rank, P.recv_ptrs, P.rcnt_ptrs, P.dec_epoch)
+
     def _mark(s, label):
         if s.events is not None:
             ev = torch.cuda.Event(enable_timing=True)
@@ -146,7 +160,13 @@ class EPLayer:
         leaves its partial output in a symmetric buffer and, after one barrier, sums all ranks' partials itself by peer
         loads in rank order (one small kernel, every rank gets bitwise the same result); two buffers alternate so that the
         barrier of the next call also protects the reads of this one.  Otherwise an all-reduce of the collective library -
-        the default: for 24 KB per token NCCL's all-reduce was measured faster than barrier + combine kernel."""
+        for 24 KB per token NCCL's all-reduce was measured faster than barrier + combine kernel.  The default with peer
+        buffers is neither: the all-reduce inside the layer kernel (fused_decode)."""
+        if s.peer is not None and s.fused_decode and s.world > 1:
+            # one kernel: every rank's partial output slices land in every rank's receive buffer as they are finished, and each
+            # rank adds them up in rank order at the end of the same launch
+            P = s.peer
+            return s.L(x, sel, rw, **({} if out is None else {"out": out}), ep=(s.world, s.rank, P.recv_ptrs, P.rcnt_ptrs, P.dec_epoch))
         if s.peer is None or not s.peer_decode or s.world == 1 or x.shape[0] > s.peer.dec[0].shape[0]:
             y = s.L(x, sel, rw) if out is None else s.L(x, sel, rw, out=out)
             if s.world > 1:

@@ -206,9 +206,11 @@ def moe_workspace(B, topk, H, I, ks_gu, ks_dn):
 
 
 def moe_forward(x, sel, rw, table, out, acc_gu, h, acc_d, cnt_gu, cnt_d, wq, I, nm_gu, nm_dn, cfg_gu, cfg_dn, G,
-                force_level, which, hits_ptr, zd, cnt_h):
+                force_level, which, hits_ptr, zd, cnt_h, ep=None):
     """One MoE layer call on the decode path, positional arguments as in the reference's moe_forward.
-    cfg_gu / cfg_dn: [k-slices per strip] (entries after the first are accepted and ignored)."""
+    cfg_gu / cfg_dn: [k-slices per strip] (entries after the first are accepted and ignored).
+    ep = (world, rank, receive-buffer addresses of all ranks, counter addresses of all ranks, epoch tensor): this rank's call of
+    an expert-parallel group, the partial outputs of all ranks summed inside the kernel over peer memory (nq_moe_forward_ep)."""
     _need(x, torch.float16, "x"); _need(rw, torch.float16, "rw"); _need(sel, torch.int64, "sel")
     _need(table, torch.int64, "table"); _need(out, torch.float32, "out"); _need(acc_gu, torch.float32, "acc_gu")
     _need(h, torch.float16, "h"); _need(acc_d, torch.float32, "acc_d"); _need(zd, torch.float32, "zd")
@@ -227,7 +229,15 @@ def moe_forward(x, sel, rw, table, out, acc_gu, h, acc_d, cnt_gu, cnt_d, wq, I, 
     a.B, a.topk, a.E, a.H, a.I = x.shape[0], sel.shape[1], table.shape[0], x.shape[1], I
     a.nm_gu, a.nm_dn, a.ks_gu, a.ks_dn = nm_gu, nm_dn, int(cfg_gu[0]), int(cfg_dn[0])
     a.G, a.force_level, a.which = G, force_level, which
-    check(lib().nq_moe_forward(C.byref(a), current_stream()), "moe_forward")
+    if ep is None:
+        check(lib().nq_moe_forward(C.byref(a), current_stream()), "moe_forward")
+        return
+    world, rank, recv_ptrs, cnt_ptrs, epoch = ep
+    d = capi.NqMoeEp()
+    d.world, d.rank = world, rank
+    d.peer_recv, d.peer_counters = (C.c_void_p * world)(*recv_ptrs), (C.c_void_p * world)(*cnt_ptrs)
+    d.epoch = epoch.data_ptr()
+    check(lib().nq_moe_forward_ep(C.byref(a), C.byref(d), current_stream()), "moe_forward_ep")
 
 
 def moe_forward_static(x, sel, rw, table, out, I, nm_gu, nm_dn, ks_gu, ks_dn, hits_ptr=0):

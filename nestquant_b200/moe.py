@@ -304,9 +304,9 @@ class MoELayer:
         s.table[e].copy_(entry(ex, level).to(s.table.device), non_blocking=False)
 
 
-    def __call__(s, x, sel, rw, out=None, force_level=0, which=3, cfg_gu=None, cfg_dn=None, table=None):
+    def __call__(s, x, sel, rw, out=None, force_level=0, which=3, cfg_gu=None, cfg_dn=None, table=None, ep=None):
         """x fp16 [B,H], sel int64 [B,topk], rw fp16 [B,topk] -> fp32 [B,H] (s.out[:B] unless `out` is given).
-        table: optional [E,20] override of s.table.  Enqueued on the current stream; no host sync."""
+        table: optional [E,20] override of s.table.  ep: see ext.moe_forward.  Enqueued on the current stream; no host sync."""
         assert x.dtype == torch.float16 and rw.dtype == torch.float16 and sel.dtype == torch.int64, (x.dtype, rw.dtype, sel.dtype)
         B = x.shape[0]
         assert B <= s.Bmax and sel.shape[1] == s.topk, f"layer was built for up to {s.Bmax} tokens, top-{s.topk}"
@@ -314,7 +314,7 @@ class MoELayer:
         ks = s.M.default_ksplit(B, s.H, s.I, s.share)
         s.M.moe_forward(x, sel, rw, s.table if table is None else table, out, s.acc_gu, s.h, s.acc_d, s.cnt_gu, s.cnt_d,
                         s.wq, s.I, s.nm_gu, s.nm_dn, cfg_gu or s.cfg_gu or [ks[0]], cfg_dn or s.cfg_dn or [ks[1]], s.G,
-                        force_level, which, s.hits_ptr, s.zd, s.cnt_h)
+                        force_level, which, s.hits_ptr, s.zd, s.cnt_h, **({} if ep is None else {"ep": ep}))
         return out
 
 
@@ -322,12 +322,12 @@ class MoELayer:
         """0, or 1 if a device-side wait of a decode-path call ran out (its outputs are then invalid).  Synchronises."""
         return int(s.cnt_h[0].item())
 
-    def capture(s, B, with_mailbox=None, host_io=False):
+    def capture(s, B, with_mailbox=None, host_io=False, ep=None):
         """Capture one B-token layer call in a CUDA graph over static buffers and return the handle:
         .x [B,H] fp16, .sel [B,topk] int64, .rw [B,topk] fp16, .out [B,H] fp32 (device), .replay().
         with_mailbox: a Mailbox whose apply() is captured in front of the layer.  host_io=True adds pinned host mirrors
         (.x_host, .sel_host, .rw_host, .out_host) and captures the host->device / device->host copies too, so one replay
-        is a complete call from host buffers."""
+        is a complete call from host buffers.  ep: see ext.moe_forward (every rank of the group must capture and replay in step)."""
         dev = s.table.device
         g = _Captured()
         # the three inputs live in one buffer (sel | x | rw, each 16-byte aligned) so that a call from host memory is a
@@ -354,7 +354,7 @@ class MoELayer:
                 g.inputs.copy_(g.inputs_host, non_blocking=True)
             if with_mailbox is not None:
                 with_mailbox.apply()
-            s(g.x, g.sel, g.rw, out=g.out)
+            s(g.x, g.sel, g.rw, out=g.out, ep=ep)
             if host_io:
                 g.out_host.copy_(g.out, non_blocking=True)
 

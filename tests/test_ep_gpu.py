@@ -51,10 +51,24 @@ def _worker(rank, world, port, q):
         yd = ep_a2a.decode(xd, seld, rwd).clone()
         want = full(xd, seld, rwd).cpu().numpy()
         res["decode_err"] = layer_errors(yd.cpu().numpy(), want)[1]
-        yp = [ep_peer.decode(xd, seld, rwd).clone() for _ in range(3)]          # alternating buffers, one barrier per call
+        # the all-reduce inside the layer kernel (default with peer buffers): several calls in a row alternate the buffer halves;
+        # a token whose picks all belong to the other rank makes this rank send a zero slice
+        yp = [ep_peer.decode(xd, seld, rwd).clone() for _ in range(5)]
         torch.cuda.synchronize()
         res["decode_peer_err"] = max(layer_errors(y.cpu().numpy(), want)[1] for y in yp)
-        res["decode_peer_same"] = bool(torch.equal(yp[0], yp[1])) and bool(torch.equal(yp[1], yp[2]))
+        res["decode_peer_same"] = all(bool(torch.equal(yp[0], y)) for y in yp[1:])
+        sel_one = torch.tensor([[0, 1, 2], [5, 6, 7], [3, 4, 0]]).to(dev)         # token 0: rank 0 only, token 1: rank 1 only (2 ranks)
+        y1 = ep_peer.decode(xd, sel_one, rwd).clone()
+        res["decode_one_sided_err"] = layer_errors(y1.cpu().numpy(), full(xd, sel_one, rwd).cpu().numpy())[1]
+        allr = [torch.empty_like(y1) for _ in range(world)]
+        dist.all_gather(allr, y1)
+        res["decode_same_on_all_ranks"] = all(bool(torch.equal(allr[0], t)) for t in allr[1:])
+        res["decode_status"] = part.status()
+        # the variant with a barrier kernel and a sum kernel
+        ep_bar = EPLayer(part, rank, world, peer_rows=64, peer_decode=True, fused_decode=False)
+        yb = [ep_bar.decode(xd, seld, rwd).clone() for _ in range(3)]
+        torch.cuda.synchronize()
+        res["decode_barrier_err"] = max(layer_errors(y.cpu().numpy(), want)[1] for y in yb)
         q.put((rank, res))
     finally:
         dist.destroy_process_group()
@@ -76,7 +90,8 @@ def test_prefill_combine_over_peer_memory():
     for rank, r in out.items():
         assert r["peer_on"] and r["combine"] == "peer loads" and r["dispatch"] == "peer loads", (rank, r)
         assert r["same"] and r["err"] <= 1e-4 and r["decode_err"] <= 1e-4 and not r["timed_out"], (rank, r)
-        assert r["decode_peer_err"] <= 1e-4 and r["decode_peer_same"], (rank, r)
+        assert r["decode_peer_err"] <= 1e-4 and r["decode_peer_same"] and r["decode_barrier_err"] <= 1e-4, (rank, r)
+        assert r["decode_one_sided_err"] <= 1e-4 and r["decode_same_on_all_ranks"] and r["decode_status"] == 0, (rank, r)
 
 
 def test_exchange_kernels_on_one_gpu():
