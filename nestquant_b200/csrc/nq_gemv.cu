@@ -560,8 +560,7 @@ __device__ __forceinline__ void ep_send(const MoeArgs& a, const Shape& sh, int p
 {
     const size_t at = (((size_t)par * a.world + a.rank) * kEpTokens + b) * a.H + grp * 128 + lane * 4;
     for (int p = 0; p < a.world; ++p) *(float4*)(a.recv[p] + at) = make_float4(o[0], o[1], o[2], o[3]);
-    __threadfence_system();
-    __syncwarp();
+    __syncwarp();       // the lanes' stores happen before the releasing adds below, which publish them (cumulativity)
     if (lane < a.world)
         asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(a.rcnt[lane] + (par * kEpTokens + b) * kEpGroups + grp) : "memory");
 }
@@ -583,8 +582,9 @@ __device__ __forceinline__ bool ep_sum(const MoeArgs& a, const Shape& sh, int pa
             if (t0 == 0) t0 = t;
             else if (t - t0 > kWaitNs) { atomicExch(a.status, 1); return false; }
         }
-        __nanosleep(100);
+        if (i > 8) __nanosleep(50);
     }
+    __syncwarp();
     float o[4] = {0.f, 0.f, 0.f, 0.f};
     for (int p = 0; p < a.world; ++p)
     {
@@ -814,15 +814,10 @@ __global__ void __launch_bounds__(kThreads, NQ_GEMV_MINBLOCKS) moe_decode_kernel
         }
     }
     // this rank's pieces are done (or handed out): add up the slices of all ranks, one (token, group) at a time
+    // (tasks are dealt out by warp index: there are more warps than tasks for every supported shape, and no counter to fight over)
     if (ep)
-        for (;;)
-        {
-            int task = 0;
-            if (lane == 0) task = atomicAdd(a.wq + 3, 1);
-            task = __shfl_sync(0xffffffffu, task, 0);
-            if (task >= a.B * sh.ngH) break;
+        for (int task = (int)blockIdx.x * kWarps + warp; task < a.B * sh.ngH; task += nwarps)
             if (!ep_sum(a, sh, par, task / sh.ngH, task % sh.ngH, lane)) break;
-        }
     // the last CTA to leave resets the queue and the per-run counters (graph replays start from zero)
     __syncthreads();
     if (threadIdx.x == 0)
