@@ -235,7 +235,8 @@ def base_code(p):
 
 
 def entry(ex, level):
-    """device table row (int64 [20]) of an expert at a level"""
+    """device table row (int64 [20]) of an expert at a level.  The field order is the table contract the kernels and the
+    serving side share (sm120/nqmoe.cu:26-45, sm120/moe.py:216-229): this function fills the fields in that order."""
     e = torch.zeros(TBL_W, dtype=torch.int64)
     e[0] = level
     for off, p in ((1, ex.gu), (5, ex.dn)):
@@ -479,7 +480,9 @@ class _Captured:
 
 
 class Mailbox:
-    """Graph-safe table updates: call .apply() inside the captured graph before the layer; stage rows from a side stream."""
+    """Graph-safe table updates: call .apply() inside the captured graph before the layer; stage rows from a side stream.
+    Same protocol and attribute names as the reference's Mailbox (sm120/moe.py:329-342): stage / seq / applied /
+    applied_host are the objects its executor writes and polls."""
 
     def __init__(s, layer):
         E, dev = layer.E, layer.table.device

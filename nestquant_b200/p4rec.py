@@ -21,7 +21,9 @@ def _up(n, a):
 
 
 def layout(ex, H, I):
-    """segment (offset, bytes) table and record size for the experts of a layer (sizes depend only on shapes and codes)"""
+    """segment (offset, bytes) table and record size for the experts of a layer (sizes depend only on shapes and codes).
+    A byte contract with the reference's record files: segment order, the 256-byte segment alignment and the 4 KiB record
+    alignment are those of streaming/p4rec.py:13-26, so this function walks the segments in the schema's order."""
     n = {"gu.p4": ex.gu.p4.numel() * 4, "gu.d4": ex.gu.d4.numel() * 4, "dn.p4": ex.dn.p4.numel() * 4,
          "dn.d4": ex.dn.d4.numel() * 4, "lr4": RMAX * (2 * I + H) * 2}
     seg, o = {}, 0
@@ -49,7 +51,8 @@ def pack(ex, lay, pin=True):
 
 def row(ex, lay, slot_ptr, entry):
     """level-4 table row whose residual pointers point into a slot holding the expert's record; the resident planes
-    (base, signs, scales, low-rank base part) stay where they are.  entry = nestquant_b200.moe.entry"""
+    (base, signs, scales, low-rank base part) stay where they are.  entry = nestquant_b200.moe.entry.  Which table fields are
+    patched, and with which segment, is the reference's schema (streaming/p4rec.py:29-37)."""
     r = entry(ex, 4)
     s = lay["seg"]
     r[2], r[3], r[6], r[7] = (slot_ptr + s[k][0] for k in ("gu.p4", "gu.d4", "dn.p4", "dn.d4"))

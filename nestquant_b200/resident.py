@@ -27,7 +27,9 @@ def lr_len(H, I, rg, rd):
 
 def save(layer, path):
     """layer: .L, .rank, .tp, .H, .I, .experts (ids), .ex {id: expert}, optional .had_dn.  An expert needs gu / dn with
-    base, var, rk (bk optional), sc {2: scales, 4: scales}, lr (or None), rg, rd."""
+    base, var, rk (bk optional), sc {2: scales, 4: scales}, lr (or None), rg, rd.
+    The dictionary keys, tensor shapes and the write-then-rename step are the file format of the reference's writer
+    (streaming/resident.py:17-33): files written here load there and the other way round (tests/test_formats_cpu.py)."""
     E = list(layer.experts)
     ex = [layer.ex[e] for e in E]
     H, I = layer.H, layer.I
