@@ -51,7 +51,6 @@ constexpr int kWarps = NQ_GEMV_WARPS, kThreads = 32 * kWarps;
 static_assert(kThreads >= NQ_MAX_PICKS, "the run list is built by one thread per pick");
 constexpr int kRunTiles = 4;     // column tiles (8 tokens each) of mma.m16n8k16 per run
 constexpr int kRunTokens = 8 * kRunTiles;
-constexpr int kRotBlocks = 4;    // 128-blocks per rotation piece
 constexpr unsigned long long kWaitNs = 2000000000ull;
 constexpr int kEpRanks = 8, kEpTokens = NQ_MAX_TOKENS, kEpGroups = 64;   // limits of the in-kernel all-reduce
 
@@ -395,11 +394,23 @@ __device__ __forceinline__ void store4h_operand(__half* chunk, int lane, const f
 
 struct Shape
 {
-    int S, ng, ngH, KSg, KSd, nparts, nruns;
+    int S, ng, ngH, KSg, KSd, nparts, rot_blocks, nruns;
     int n_rot, n_gu, n_dn, per_run_gu, per_run_dn;
 };
 
-// ---------------------------------------------------------------- rotation piece: (pick, blocks [4 part, 4 part + 4))
+// ---------------------------------------------------------------- rotation piece: (pick, blocks [rb part, rb part + rb))
+// rb = 1 whenever there are at least as many warps as (pick, block) pairs: every gate|up piece waits for the rotations, so
+// they are spread as thin as possible, and the inputs of the next block are fetched before the current one is transformed.
+struct RotIn { uint2 x, g, u; };
+__device__ __forceinline__ RotIn rot_fetch(const __half* xr, const __half* scales, const __half* su_u, int k)
+{
+    return RotIn{*(const uint2*)(xr + k), *(const uint2*)(scales + k), *(const uint2*)(su_u + k)};
+}
+__device__ __forceinline__ void unpack4h(const uint2& w, float (&f)[4])
+{
+    const __half2 a = *(const __half2*)&w.x, b = *(const __half2*)&w.y;
+    f[0] = __low2float(a); f[1] = __high2float(a); f[2] = __low2float(b); f[3] = __high2float(b);
+}
 __device__ __forceinline__ void rotate_piece(const MoeArgs& a, const Shape& sh, const Route& R, int piece, int lane)
 {
     const int s = piece / sh.nparts, part = piece - s * sh.nparts;
@@ -410,12 +421,14 @@ __device__ __forceinline__ void rotate_piece(const MoeArgs& a, const Shape& sh, 
         const __half* su_u = scales + 2 * a.H + 3 * a.I;
         const __half* xr = a.x + (size_t)(s / a.topk) * a.H;
         __half* dst = a.xrot + (size_t)s * 2 * a.H;
-        const int b1 = (part + 1) * kRotBlocks < a.H / 128 ? (part + 1) * kRotBlocks : a.H / 128;
-        for (int blk = part * kRotBlocks; blk < b1; ++blk)
+        const int b0 = part * sh.rot_blocks, b1 = b0 + sh.rot_blocks < sh.ngH ? b0 + sh.rot_blocks : sh.ngH;
+        RotIn in = rot_fetch(xr, scales, su_u, b0 * 128 + lane * 4);
+        for (int blk = b0; blk < b1; ++blk)
         {
-            const int k = blk * 128 + lane * 4;
+            const RotIn cur = in;
+            if (blk + 1 < b1) in = rot_fetch(xr, scales, su_u, (blk + 1) * 128 + lane * 4);
             float f[4], g[4], u[4];
-            load4h(xr + k, f); load4h(scales + k, g); load4h(su_u + k, u);
+            unpack4h(cur.x, f); unpack4h(cur.g, g); unpack4h(cur.u, u);
             float vg[4] = {f[0] * g[0], f[1] * g[1], f[2] * g[2], f[3] * g[3]};
             float vu[4] = {f[0] * u[0], f[1] * u[1], f[2] * u[2], f[3] * u[3]};
             wht128(vg, lane); wht128(vu, lane);
@@ -691,11 +704,12 @@ __device__ __forceinline__ bool gemv_piece(const MoeArgs& a, const Shape& sh, co
     return true;
 }
 
-__device__ __forceinline__ Shape make_shape(const MoeArgs& a, int nruns)
+__device__ __forceinline__ Shape make_shape(const MoeArgs& a, int nruns, int nwarps)
 {
     Shape sh;
     sh.S = a.B * a.topk; sh.ng = a.I / 128; sh.ngH = a.H / 128; sh.KSg = a.ks_gu; sh.KSd = a.ks_dn;
-    sh.nparts = (sh.ngH + kRotBlocks - 1) / kRotBlocks; sh.nruns = nruns;
+    sh.rot_blocks = (sh.S * sh.ngH + nwarps - 1) / nwarps;
+    sh.nparts = (sh.ngH + sh.rot_blocks - 1) / sh.rot_blocks; sh.nruns = nruns;
     sh.per_run_gu = sh.ng * 2 * sh.KSg * 8; sh.per_run_dn = sh.ngH * sh.KSd * 8;
     sh.n_rot = (a.which & 1) ? sh.S * sh.nparts : 0;
     sh.n_gu = (a.which & 1) ? nruns * sh.per_run_gu : 0;
@@ -712,7 +726,8 @@ __global__ void __launch_bounds__(kThreads, NQ_GEMV_MINBLOCKS) moe_decode_kernel
     grid_dependency_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     build_route(a, R);
-    const Shape sh = make_shape(a, R.nruns);
+    const int nwarps = (int)gridDim.x * kWarps;
+    const Shape sh = make_shape(a, R.nruns, nwarps);
     if (blockIdx.x == 0 && a.hits && (int)threadIdx.x < sh.S)
     {
         const int64_t es = a.sel[threadIdx.x];
@@ -744,7 +759,6 @@ __global__ void __launch_bounds__(kThreads, NQ_GEMV_MINBLOCKS) moe_decode_kernel
     int ready_run = -1;        // the run whose h this warp has seen complete
     // a warp's first piece is its own index (thousands of warps start at once: no burst of atomics on one address); later
     // ones come from the queue counter, which therefore counts from the number of warps
-    const int nwarps = (int)gridDim.x * kWarps;
     for (int round = 0;; ++round)
     {
         int piece = (int)blockIdx.x * kWarps + warp;
