@@ -11,6 +11,9 @@
 #include "nq_format.cuh"
 #include "nq_rotate.cuh"
 
+#ifndef NQ_PF_PRE_BLOCKS
+#define NQ_PF_PRE_BLOCKS 2    // pf_pre keeps two scale vectors and a prefetched row in registers
+#endif
 #ifndef NQ_PF_EW_BLOCKS
 #define NQ_PF_EW_BLOCKS 3     // resident 256-thread CTAs the elementwise passes are compiled for (register cap)
 #endif
@@ -57,53 +60,90 @@ __device__ __forceinline__ const __half* token_row(const TokenRows& r, int t, in
     return r.base[owner] + (size_t)(t - owner * r.tokens_per_rank) * H;
 }
 
-// one CTA per pair, one warp per 1024 columns
-__global__ void __launch_bounds__(256, NQ_PF_EW_BLOCKS) pf_pre_kernel(TokenRows rows, const int* __restrict__ pt, const int* __restrict__ pe,
-                                                     const int64_t* __restrict__ table, int E, __half* xg, __half* xu, float* zg, int H, int I, int kperm)
+// A CTA takes a contiguous range of the (expert-sorted) pairs, a warp 1,024 columns of every one of them.  The two scale
+// vectors of those columns stay in registers while the expert stays the same (the pairs of an expert are consecutive),
+// and the input row of the next pair is fetched before the current one is transformed.
+struct PairHead { int e; bool live; const __half* xr; const int64_t* row; int level; };
+__device__ __forceinline__ PairHead pair_head(const TokenRows& rows, const int* __restrict__ pt, const int* __restrict__ pe,
+                                              const int64_t* __restrict__ table, int E, int H, int p, int p1)
 {
-    const int p = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-    if (pe[p] < 0 || pe[p] >= E) return;      // a pick with no valid expert id (padding): nothing to prepare
-    const int64_t* row = table + (int64_t)pe[p] * kTableWidth;
-    const int level = (int)row[0];
-    if (level <= 0) return;
-    const __half* scales = (const __half*)row[9];
-    const __half* su_u = scales + 2 * H + 3 * I;
-    const __half* xr = token_row(rows, pt[p], H);
-    const int ng = H / 128;
+    PairHead h{-1, false, nullptr, nullptr, 0};
+    if (p >= p1) return h;
+    h.e = pe[p];
+    if (h.e < 0 || h.e >= E) return h;           // a pick with no valid expert id (padding): nothing to prepare
+    h.row = table + (int64_t)h.e * kTableWidth;
+    h.level = (int)h.row[0];
+    if (h.level <= 0) return h;
+    h.live = true;
+    h.xr = token_row(rows, pt[p], H);
+    return h;
+}
+__global__ void __launch_bounds__(256, NQ_PF_PRE_BLOCKS) pf_pre_kernel(TokenRows rows, const int* __restrict__ pt, const int* __restrict__ pe,
+                                                     const int64_t* __restrict__ table, int E, __half* xg, __half* xu, float* zg, int H, int I,
+                                                     int kperm, int R)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5, ng = H / 128;
+    const int per = (R + (int)gridDim.x - 1) / (int)gridDim.x, p0 = (int)blockIdx.x * per, p1 = p0 + per < R ? p0 + per : R;
+    const int q = lane & 3;
     for (int g0 = warp * 8; g0 < ng; g0 += nwarp * 8)
     {
-        const int grp = g0 + (lane >> 2), k = grp * 128, q = lane & 3;
-        const bool live = grp < ng;
-        uint32_t xw[16];
-        float v[32];
-        if (live) load16w_mapH(xr + k, q, xw);
-#pragma unroll
-        for (int up = 0; up < 2; ++up)
+        const int grp = g0 + (lane >> 2), k = grp * 128;
+        const bool in_row = grp < ng;
+        uint32_t sg[16], su[16], xw[16];
+        int have = -1;                               // expert whose scales sg / su hold
+        PairHead cur = pair_head(rows, pt, pe, table, E, H, p0, p1);
+        if (cur.live && in_row) load16w_mapH(cur.xr + k, q, xw);
+        for (int p = p0; p < p1; ++p)
         {
-            if (live) mul32h_mapH(xw, (up ? su_u : scales) + k, q, v);
-            else
+            const PairHead nxt = pair_head(rows, pt, pe, table, E, H, p + 1, p1);
+            if (cur.live)
+            {
+                if (cur.e != have)
+                {
+                    const __half* scales = (const __half*)cur.row[9];
+                    if (in_row) { load16w_mapH(scales + k, q, sg); load16w_mapH(scales + 2 * H + 3 * I + k, q, su); }
+                    have = cur.e;
+                }
+                float v[32];
+                if (in_row) mul32w_mapH(xw, sg, v);
+                else
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0.f;
-            wht128_x8(v, lane);
-            if (kperm) store32h_mapH_kperm((up ? xu : xg) + (size_t)p * H + k, q, v, live);
-            else if (live) store32h_mapH((up ? xu : xg) + (size_t)p * H + k, q, v);
+                    for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                wht128_x8(v, lane);
+                if (kperm) store32h_mapH_kperm(xg + (size_t)p * H + k, q, v, in_row);
+                else if (in_row) store32h_mapH(xg + (size_t)p * H + k, q, v);
+                if (in_row) mul32w_mapH(xw, su, v);
+                // the row is consumed: fetch the next pair's while the second half of this one is transformed
+                if (nxt.live && in_row) load16w_mapH(nxt.xr + k, q, xw);
+                wht128_x8(v, lane);
+                if (kperm) store32h_mapH_kperm(xu + (size_t)p * H + k, q, v, in_row);
+                else if (in_row) store32h_mapH(xu + (size_t)p * H + k, q, v);
+            }
+            else if (nxt.live && in_row) load16w_mapH(nxt.xr + k, q, xw);
+            cur = nxt;
         }
     }
-    const LowRank L = low_rank_of(row, level);
-    for (int r = warp; r < 4; r += nwarp)
+    // low-rank inputs z_gu = x V_gu^T: warp r of the CTA takes component r of every pair
+    for (int p = p0; p < p1; ++p)
     {
-        float d = 0.f;
-        if (r < L.rg)
+        const PairHead hd = pair_head(rows, pt, pe, table, E, H, p, p1);
+        if (!hd.live) continue;
+        const LowRank L = low_rank_of(hd.row, hd.level);
+        for (int r = warp; r < 4; r += nwarp)
         {
-            for (int k = lane * 4; k < H; k += 128)
+            float d = 0.f;
+            if (r < L.rg)
             {
-                float f[4], v[4];
-                load4h(xr + k, f); load4h(L.lr + (size_t)r * H + k, v);
-                d += f[0] * v[0] + f[1] * v[1] + f[2] * v[2] + f[3] * v[3];
+                for (int k = lane * 4; k < H; k += 128)
+                {
+                    float f[4], v[4];
+                    load4h(hd.xr + k, f); load4h(L.lr + (size_t)r * H + k, v);
+                    d += f[0] * v[0] + f[1] * v[1] + f[2] * v[2] + f[3] * v[3];
+                }
+                d = warp_sum(d);
             }
-            d = warp_sum(d);
+            if (lane == 0) zg[(size_t)p * 4 + r] = d;
         }
-        if (lane == 0) zg[(size_t)p * 4 + r] = d;
     }
 }
 
@@ -303,6 +343,15 @@ __global__ void pf_hits_kernel(const int* __restrict__ counts, int* hits, int E)
 }
 
 // threads per CTA of the passes above: one warp per 1024 columns of the row, at most 8 warps
+// CTAs of pf_pre: enough to fill the device a few times over, each with a run of consecutive pairs
+static int pf_pre_grid(int R)
+{
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int want = (sms > 0 ? sms : 148) * NQ_PF_PRE_BLOCKS * 4;
+    return R < want ? R : want;
+}
 static int pf_threads(int cols) { const int w = (cols + 1023) / 1024; return 32 * (w > 8 ? 8 : w); }
 
 }  // namespace nq
@@ -322,7 +371,7 @@ int nq_pf_pre(const void* x, const int32_t* pt, const int32_t* pe, int R, const 
     NQ_REQUIRE(nq::aligned16(x) && nq::aligned16(xg) && nq::aligned16(xu), "nq_pf_pre: x, xg, xu must be 16-byte aligned");
     nq::TokenRows rows{};
     rows.base[0] = (const __half*)x; rows.tokens_per_rank = 0x7fffffff;
-    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>(rows, pt, pe, table, E, (__half*)xg, (__half*)xu, zg, H, I, kperm);
+    nq::pf_pre_kernel<<<nq::pf_pre_grid(R), nq::pf_threads(H), 0, (cudaStream_t)stream>>>(rows, pt, pe, table, E, (__half*)xg, (__half*)xu, zg, H, I, kperm, R);
     return nq::check_launch("nq_pf_pre");
 }
 
@@ -343,7 +392,7 @@ int nq_pf_pre_ep(const void* const* peer_x, int world, int tokens_per_rank, cons
         rows.base[r] = (const __half*)peer_x[r];
     }
     rows.tokens_per_rank = tokens_per_rank;
-    nq::pf_pre_kernel<<<R, nq::pf_threads(H), 0, (cudaStream_t)stream>>>(rows, pt, pe, table, E, (__half*)xg, (__half*)xu, zg, H, I, kperm);
+    nq::pf_pre_kernel<<<nq::pf_pre_grid(R), nq::pf_threads(H), 0, (cudaStream_t)stream>>>(rows, pt, pe, table, E, (__half*)xg, (__half*)xu, zg, H, I, kperm, R);
     return nq::check_launch("nq_pf_pre_ep");
 }
 

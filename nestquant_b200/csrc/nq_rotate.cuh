@@ -14,12 +14,11 @@ __device__ __forceinline__ void wht128(float (&v)[4], int lane)
     v[0] = a + c; v[1] = b + d; v[2] = a - c; v[3] = b - d;
 #pragma unroll
     for (int m = 1; m < 32; m <<= 1)
+    {
+        const float s = (lane & m) ? -1.f : 1.f;       // o - v or v + o as one fma (exact either way)
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-        {
-            const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
-            v[i] = (lane & m) ? o - v[i] : v[i] + o;
-        }
+        for (int i = 0; i < 4; ++i) v[i] = fmaf(v[i], s, __shfl_xor_sync(0xffffffffu, v[i], m));
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] *= 0.08838834764831845f;   // 1 / sqrt(128)
 }
@@ -52,12 +51,11 @@ __device__ __forceinline__ void wht128_x8(float (&v)[32], int lane)
             }
 #pragma unroll
     for (int m = 1; m < 4; m <<= 1)
+    {
+        const float s = (lane & m) ? -1.f : 1.f;       // o - v or v + o as one fma (exact either way)
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-        {
-            const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
-            v[i] = (lane & m) ? o - v[i] : v[i] + o;
-        }
+        for (int i = 0; i < 32; ++i) v[i] = fmaf(v[i], s, __shfl_xor_sync(0xffffffffu, v[i], m));
+    }
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] *= 0.08838834764831845f;
 }
@@ -192,19 +190,14 @@ __device__ __forceinline__ void load16w_mapH(const __half* p, int q, uint32_t (&
         w[4 * j] = u.x; w[4 * j + 1] = u.y; w[4 * j + 2] = u.z; w[4 * j + 3] = u.w;
     }
 }
-__device__ __forceinline__ void mul32h_mapH(const uint32_t (&xw)[16], const __half* sp, int q, float (&v)[32])
+// v = x * s for the lane's 32 elements, both given as the packed fp16 words of map H (fp32 products)
+__device__ __forceinline__ void mul32w_mapH(const uint32_t (&xw)[16], const uint32_t (&sw)[16], float (&v)[32])
 {
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int i = 0; i < 16; ++i)
     {
-        const uint4 u = *(const uint4*)(sp + 32 * j + 8 * q);
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-        {
-            const __half2 a = *(const __half2*)&xw[4 * j + i], b = *(const __half2*)&w[i];
-            v[8 * j + 2 * i] = __low2float(a) * __low2float(b); v[8 * j + 2 * i + 1] = __high2float(a) * __high2float(b);
-        }
+        const __half2 a = *(const __half2*)&xw[i], b = *(const __half2*)&sw[i];
+        v[2 * i] = __low2float(a) * __low2float(b); v[2 * i + 1] = __high2float(a) * __high2float(b);
     }
 }
 template <class F>
