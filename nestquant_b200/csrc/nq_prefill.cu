@@ -5,7 +5,7 @@
 //   pf_combine  out[token]  = sum over the token's picks in pick order     (no atomics: bitwise repeatable)
 //   pf_hits     routing-hit export
 // Replaces nq_pf_pre / nq_pf_mid / nq_pf_post / nq_pf_hits of the reference (sm120/nqmoe.cu:1081-1245,1258-1293).
-// All of them are HBM-bound elementwise passes over [pairs][H] or [pairs][I] arrays; a CTA owns a pair (or a token), a
+// All of them are elementwise passes over [pairs][H] or [pairs][I] arrays; a CTA owns a pair, a token or (pf_pre) a run of pairs, a
 // warp eight 128-wide groups (Hadamard blocks) at a time, 32 consecutive columns per lane.
 #include "nq_common.cuh"
 #include "nq_format.cuh"
