@@ -256,10 +256,12 @@ class EPLayer:
         st = torch.cuda.current_stream(dev).cuda_stream
         s._mark("start")
         P.xbuf[:T].copy_(x)
-        sel_all = torch.empty(W * T, k, dtype=sel.dtype, device=dev)
-        rw_all = torch.empty(W * T, k, dtype=rw.dtype, device=dev)
-        dist.all_gather_into_tensor(sel_all, sel.contiguous(), group=s.group)
-        dist.all_gather_into_tensor(rw_all, rw.contiguous(), group=s.group)
+        # one collective for both: the expert id in the low 32 bits (two's complement), the fp16 weight in bits 32..47
+        packed = (sel & 0xFFFFFFFF) | (rw.contiguous().view(torch.int16).to(torch.int64) & 0xFFFF) << 32
+        packed_all = torch.empty(W * T, k, dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(packed_all, packed.contiguous(), group=s.group)
+        sel_all = (packed_all << 32) >> 32                                         # sign-extends padded (negative) ids
+        rw_all = (packed_all >> 32).to(torch.int16).view(torch.float16)
         owner = torch.div(sel_all, s.per, rounding_mode="floor")
         rw_mine = torch.where(owner == s.rank, rw_all, torch.zeros_like(rw_all))
         P.barrier()                                                                # every rank's input rows are in place
@@ -268,10 +270,9 @@ class EPLayer:
         s._mark("local prefill (dispatch by peer loads in its first pass)")
         mine = owner[s.rank * T:(s.rank + 1) * T]                                  # ranks that hold a pick of my tokens
         live = rw != 0
-        rows = torch.full((W, T), -1, dtype=torch.int32, device=dev)
         tok = torch.arange(s.rank * T, (s.rank + 1) * T, dtype=torch.int32, device=dev)
-        for d in range(W):
-            rows[d] = torch.where(((mine == d) & live).any(1), tok, rows[d])
+        held = (torch.where(live, mine, -1).unsqueeze(0) == torch.arange(W, device=dev).view(W, 1, 1)).any(2)   # [W, T]
+        rows = torch.where(held, tok.unsqueeze(0), -1).to(torch.int32).contiguous()
         out = torch.empty(T, s.H, dtype=torch.float32, device=dev)
         P.barrier()                                                                # every rank's partial rows are complete
         pp = (C.c_void_p * W)(*P.part_ptrs)
