@@ -194,7 +194,7 @@ def default_ksplit(B, H, I, share=1.0):
                 return k
         return 1
     load = B * share
-    want_gu, want_dn = (8, 4) if load <= 0.5 else (4, 2) if load <= 2 else (2, 1) if load <= 8 else (1, 1)
+    want_gu, want_dn = (8, 4) if load <= 0.5 else (4, 2) if load <= 1 else (2, 1) if load <= 4 else (1, 1)
     return pick(H // 128, want_gu), pick(I // 128, want_dn)
 
 
