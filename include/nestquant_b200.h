@@ -259,6 +259,14 @@ int nq_salience(const void* x, int x_is_bf16, int64_t row_stride, const void* rw
 int nq_ep_gather(void* xstage, const void* const* peer_x, const int64_t* sel, const void* rw, int tokens_per_rank, int topk, int H,
                  int world, int rank, int experts_per_rank, void* stream);
 
+/* The picks of every rank's tokens, fetched from the ranks' buffers (plain peer loads; the caller's nq_ep_barrier makes
+ * them complete first): peer_sel[w] / peer_rw[w] = int64 / fp16 [tokens_per_rank][topk] of rank w, as seen from this GPU
+ * (host arrays of `world` device addresses).  sel_all (int64 [world * tokens_per_rank][topk]) gets every pick's expert id;
+ * rw_mine (fp16, same shape) its weight where the expert belongs to this rank (id / experts_per_rank == rank), else 0.
+ * Takes the place of an all-gather of the picks and the masking that follows it.  No counterpart in the reference. */
+int nq_ep_picks(const int64_t* const* peer_sel, const void* const* peer_rw, int tokens_per_rank, int topk, int world, int rank,
+                int experts_per_rank, int64_t* sel_all, void* rw_mine, void* stream);
+
 /* Barrier over the ranks of an expert-parallel group, as one small kernel per rank on `stream`: rank `rank` stores its call
  * number (*epoch + 1) into flag [rank] of every peer_flags[r] (int32 [world] per rank, zero-initialised symmetric memory;
  * host array of `world` device addresses as seen from this GPU), waits until its own flags have all reached that number,

@@ -80,6 +80,7 @@ SIGNATURES = {
     "nq_moe_forward_static": (_i, [_p, _p, _p, _p, _p] + [_i] * 9 + [_p, _p]),
     "nq_salience": (_i, [_p, _i, _i64, _p, _p, _i, _i, _i, _i, C.c_float, _p, _p, _p]),
     "nq_ep_barrier": (_i, [C.POINTER(_p), _i, _i, _p, _p, C.c_longlong, _p]),
+    "nq_ep_picks": (_i, [C.POINTER(_p), C.POINTER(_p), _i, _i, _i, _i, _i, _p, _p, _p]),
     "nq_ep_gather": (_i, [_p, C.POINTER(_p), _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "nq_ep_combine": (_i, [_p, C.POINTER(_p), _p, _i, _i, _i, _p]),
     "nq_engine_open": (_i, [C.c_char_p, C.c_char_p, _sz, _i, _i, _i, _i, C.POINTER(_p)]),

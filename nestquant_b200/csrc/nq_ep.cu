@@ -103,6 +103,25 @@ __global__ void __launch_bounds__(32) ep_barrier_kernel(EpFlags peers, int rank,
     if (r == 0) *epoch = e;
 }
 
+// The picks of every rank's tokens, read from the ranks' buffers: sel_all[w * T + t][k] = sel of rank w's token t;
+// rw_mine = its weight where the pick belongs to one of this rank's experts, else 0 (other ranks' picks then sort away
+// in this rank's prefill).
+struct EpPicks { const int64_t* sel[kEpMaxRanks]; const __half* rw[kEpMaxRanks]; };
+__global__ void __launch_bounds__(256) ep_picks_kernel(EpPicks peers, int n_per_rank, int world, int rank, int per, int64_t* __restrict__ sel_all,
+                                                       __half* __restrict__ rw_mine)
+{
+    const int n = n_per_rank * world;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    {
+        const int w = i / n_per_rank, j = i - w * n_per_rank;
+        const int64_t e = peers.sel[w][j];
+        const __half r = peers.rw[w][j];
+        sel_all[i] = e;
+        const bool mine = e >= 0 && e / per == rank;
+        rw_mine[i] = mine ? r : __ushort_as_half((unsigned short)0);
+    }
+}
+
 }  // namespace nq
 
 extern "C" int nq_ep_barrier(int32_t* const* peer_flags, int rank, int world, int32_t* epoch, int32_t* status, long long timeout_ns,
@@ -118,6 +137,26 @@ extern "C" int nq_ep_barrier(int32_t* const* peer_flags, int rank, int world, in
     }
     nq::ep_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, rank, world, epoch, status, (unsigned long long)timeout_ns);
     return nq::check_launch("nq_ep_barrier");
+}
+
+extern "C" int nq_ep_picks(const int64_t* const* peer_sel, const void* const* peer_rw, int tokens_per_rank, int topk, int world, int rank,
+                           int experts_per_rank, int64_t* sel_all, void* rw_mine, void* stream)
+{
+    NQ_REQUIRE(tokens_per_rank >= 0 && topk >= 1 && world >= 1 && world <= nq::kEpMaxRanks && rank >= 0 && rank < world && experts_per_rank >= 1,
+               "nq_ep_picks: bad shape (tokens %d, topk %d, world %d, rank %d)", tokens_per_rank, topk, world, rank);
+    if (tokens_per_rank == 0) return NQ_OK;
+    NQ_REQUIRE(peer_sel && peer_rw && sel_all && rw_mine, "nq_ep_picks: null pointer");
+    NQ_REQUIRE((long long)tokens_per_rank * topk * world < (1ll << 31), "nq_ep_picks: too many picks");
+    nq::EpPicks p{};
+    for (int r = 0; r < world; ++r)
+    {
+        NQ_REQUIRE(peer_sel[r] && peer_rw[r], "nq_ep_picks: buffer of rank %d is null", r);
+        p.sel[r] = peer_sel[r]; p.rw[r] = (const __half*)peer_rw[r];
+    }
+    const int n = tokens_per_rank * topk * world, blocks = (n + 255) / 256;
+    nq::ep_picks_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, (cudaStream_t)stream>>>(p, tokens_per_rank * topk, world, rank, experts_per_rank,
+                                                                                        sel_all, (__half*)rw_mine);
+    return nq::check_launch("nq_ep_picks");
 }
 
 extern "C" int nq_ep_gather(void* xstage, const void* const* peer_x, const int64_t* sel, const void* rw, int tokens_per_rank, int topk, int H,

@@ -61,11 +61,15 @@ def _exchange_counts(counts, group):
     return torch.stack(allc).cpu().tolist()
 
 
+PICKS_MAX = 16        # picks per token that the symmetric pick buffers are sized for
+
+
 class PeerBuffers:
     """Symmetric-memory buffers of one rank, with every rank's address of each, and a barrier of our own over them.
 
     part   fp32 [rows, H]      partial output rows of the prefill (row = global token)
     xbuf   fp16 [rows_x, H]    this rank's input rows, read by the peers' first prefill pass
+    sel, rw  int64 / fp16 [rows_x * 16]   this rank's picks, read by the peers before they sort (nq_ep_picks)
     dec    2 x fp32 [32, H]    partial outputs of the decode path (alternating), for the barrier + sum-kernel variant
     recv   fp32 [2, world, 32, H], rcnt int32 [2, 32 * 64]   receive slots and arrival counters of the in-kernel all-reduce
     flags  int32 [8]           barrier flags: flag [r] = last call number rank r announced to this rank
@@ -86,6 +90,8 @@ class PeerBuffers:
         s.part, s.part_ptrs = shared(rows, H, dtype=torch.float32)
         s.rows_x = (rows + world - 1) // world
         s.xbuf, s.x_ptrs = shared(s.rows_x, H, dtype=torch.float16)
+        s.sel, s.sel_ptrs = shared(s.rows_x * PICKS_MAX, dtype=torch.int64)      # this rank's picks, read by the peers
+        s.rw, s.rw_ptrs = shared(s.rows_x * PICKS_MAX, dtype=torch.float16)
         s.dec, s.dec_ptrs, s.dec_turn, s.dec_rows = [], [], 0, {}
         for _ in range(2):
             b, p = shared(32, H, dtype=torch.float32)
@@ -256,19 +262,28 @@ class EPLayer:
         st = torch.cuda.current_stream(dev).cuda_stream
         s._mark("start")
         P.xbuf[:T].copy_(x)
-        # one collective for both: the expert id in the low 32 bits (two's complement), the fp16 weight in bits 32..47
-        packed = (sel & 0xFFFFFFFF) | (rw.contiguous().view(torch.int16).to(torch.int64) & 0xFFFF) << 32
-        packed_all = torch.empty(W * T, k, dtype=torch.int64, device=dev)
-        dist.all_gather_into_tensor(packed_all, packed.contiguous(), group=s.group)
-        sel_all = (packed_all << 32) >> 32                                         # sign-extends padded (negative) ids
-        rw_all = (packed_all >> 32).to(torch.int16).view(torch.float16)
-        owner = torch.div(sel_all, s.per, rounding_mode="floor")
-        rw_mine = torch.where(owner == s.rank, rw_all, torch.zeros_like(rw_all))
-        P.barrier()                                                                # every rank's input rows are in place
+        sel_all = torch.empty(W * T, k, dtype=torch.int64, device=dev)
+        rw_mine = torch.empty(W * T, k, dtype=torch.float16, device=dev)
+        if k <= PICKS_MAX:
+            # the picks stay where they are: after the barrier every rank reads them from the owners' buffers
+            P.sel[:T * k].copy_(sel.reshape(-1))
+            P.rw[:T * k].copy_(rw.reshape(-1))
+            P.barrier()                                                            # every rank's rows and picks are in place
+            check(lib().nq_ep_picks((C.c_void_p * W)(*P.sel_ptrs), (C.c_void_p * W)(*P.rw_ptrs), T, k, W, s.rank, s.per,
+                                    sel_all.data_ptr(), rw_mine.data_ptr(), st), "ep_picks")
+        else:
+            # one collective for both: the expert id in the low 32 bits (two's complement), the fp16 weight in bits 32..47
+            packed = (sel & 0xFFFFFFFF) | (rw.contiguous().view(torch.int16).to(torch.int64) & 0xFFFF) << 32
+            packed_all = torch.empty(W * T, k, dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(packed_all, packed.contiguous(), group=s.group)
+            sel_all = (packed_all << 32) >> 32                                     # sign-extends padded (negative) ids
+            rw_all = (packed_all >> 32).to(torch.int16).view(torch.float16)
+            rw_mine = torch.where(torch.div(sel_all, s.per, rounding_mode="floor") == s.rank, rw_all, torch.zeros_like(rw_all))
+            P.barrier()                                                            # every rank's input rows are in place
         s._mark("picks gathered, inputs in place")
         s.L.prefill(x, sel_all, rw_mine, out=P.part[:W * T], x_peers=(P.x_ptrs, T))
         s._mark("local prefill (dispatch by peer loads in its first pass)")
-        mine = owner[s.rank * T:(s.rank + 1) * T]                                  # ranks that hold a pick of my tokens
+        mine = torch.div(sel, s.per, rounding_mode="floor")                        # ranks that hold a pick of my tokens
         live = rw != 0
         tok = torch.arange(s.rank * T, (s.rank + 1) * T, dtype=torch.int32, device=dev)
         held = (torch.where(live, mine, -1).unsqueeze(0) == torch.arange(W, device=dev).view(W, 1, 1)).any(2)   # [W, T]

@@ -95,7 +95,7 @@ def test_prefill_combine_over_peer_memory():
 
 
 def test_exchange_kernels_on_one_gpu():
-    """nq_ep_gather / nq_ep_combine with the buffers of three emulated ranks on one device (the kernels only see addresses):
+    """nq_ep_gather / nq_ep_picks / nq_ep_combine with the buffers of three emulated ranks on one device (the kernels only see addresses):
     the gathered rows and the rank-ordered sums must equal plain indexing."""
     import ctypes as C
     from nestquant_b200.capi import check, lib
@@ -113,6 +113,17 @@ def test_exchange_kernels_on_one_gpu():
     want = torch.where(need[:, None], torch.cat(xs), torch.full_like(stage, 7.0))
     torch.cuda.synchronize()
     assert torch.equal(stage, want) and 0 < int(need.sum()) < W * T and not bool(need[5])
+    # nq_ep_picks: every rank's picks read from the ranks' buffers, the weights of other ranks' experts zeroed
+    sels = [torch.randint(-2, W * per + 2, (T, k), generator=g).cuda() for _ in range(W)]       # some ids out of range
+    rws = [torch.rand(T, k, generator=g).half().cuda() for _ in range(W)]
+    sel_all = torch.empty(W * T, k, dtype=torch.int64, device="cuda")
+    rw_mine = torch.empty(W * T, k, dtype=torch.float16, device="cuda")
+    ps, pr = (C.c_void_p * W)(*[t.data_ptr() for t in sels]), (C.c_void_p * W)(*[t.data_ptr() for t in rws])
+    check(lib().nq_ep_picks(ps, pr, T, k, W, rank, per, sel_all.data_ptr(), rw_mine.data_ptr(), st), "ep_picks")
+    cat_sel, cat_rw = torch.cat(sels), torch.cat(rws)
+    torch.cuda.synchronize()
+    assert torch.equal(sel_all, cat_sel)
+    assert torch.equal(rw_mine, torch.where(torch.div(cat_sel, per, rounding_mode="floor") == rank, cat_rw, torch.zeros_like(cat_rw)))
     parts = [torch.randn(W * T, H, generator=g).cuda() for _ in range(W)]
     rows = torch.randint(-1, W * T, (W, T), generator=g, dtype=torch.int32).cuda()
     out = torch.empty(T, H, device="cuda")
