@@ -361,6 +361,45 @@ def ep_parity_case(rank, world, dev):
             "case": f"{NE} experts, H {H}, I {I}, top-{topk}, {T} tokens per rank against a single-GPU layer holding every expert"}
 
 
+def tp_parity_case(rank, world, dev):
+    """Tensor-parallel decode on a small layer: rank r holds shard r of every expert (an expert of I / world columns) and the
+    partial outputs are summed inside the layer kernel; the reference is the sum of all the shards' layers evaluated one
+    after the other on this GPU (every rank builds every shard, from seeds)."""
+    import torch
+    import torch.distributed as dist
+    from nestquant_b200 import moe
+    from nestquant_b200.ep import EPLayer
+    from tests.util import layer_errors
+    H, I, NE, topk, B = 1024, 1024, 16, 4, 3
+    Is = I // world
+    levels = [4 if i % 3 else 2 for i in range(NE)]
+    shards = []
+    for r in range(world):
+        Lr = moe.MoELayer(NE, H, Is, Bmax=4, topk=topk, dev=dev)
+        keep = [moe.Expert(H, Is, seed=5200 + 100 * r + i, rk_gu=0, rk_dn=7, var=True, sv=0.02, dev=dev) for i in range(NE)]
+        for e in range(NE):
+            Lr.set(e, keep[e], levels[e])
+        shards.append((Lr, keep))
+    g = torch.Generator().manual_seed(33)
+    x = torch.randn(B, H, generator=g).bfloat16().half().to(dev)
+    sel = torch.stack([torch.randperm(NE, generator=g)[:topk] for _ in range(B)]).to(dev)
+    rw = torch.softmax(torch.randn(B, topk, generator=g), 1).half().to(dev)
+    ref = torch.zeros(B, H, dtype=torch.float32, device=dev)
+    for Lr, _ in shards:                                   # rank order, as the kernel adds the slices
+        ref += Lr(x, sel, rw)[:B]
+    tp = EPLayer(shards[rank][0], rank, world, peer_rows=world, fused_decode=True)
+    y = tp.decode(x, sel, rw).clone()
+    y2 = tp.decode(x, sel, rw).clone()
+    torch.cuda.synchronize()
+    err = torch.tensor([layer_errors(y.cpu().numpy(), ref.cpu().numpy())[1], float(not torch.equal(y, y2)),
+                        float(tp.peer is None or tp.peer.timed_out()), float(shards[rank][0].status())], dtype=torch.float64, device=dev)
+    dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    e = err.tolist()
+    return {"decode_rel_l2": e[0], "repeatable": e[1] == 0, "no_peer_buffers_or_timed_out": bool(e[2]), "device_status": int(e[3]),
+            "ok": bool(e[0] <= 2e-3 and e[1] == 0 and e[2] == 0 and e[3] == 0),
+            "case": f"{NE} experts, H {H}, I {I} cut into {world} shards, top-{topk}, {B} tokens against the sum of the shards' layers on one GPU"}
+
+
 def layer_stack_case(cfg, rank, world, dev, n_layers=16, window=65536):
     """Config 4 of the workload list: a stack of 16 consecutive GLM-5-shaped MoE layers with a seeded mixed level map per
     layer (25 % level 2, 25 % level 4 with half of the chunks refined = "3-bit", 50 % level 4), experts split contiguously
@@ -524,7 +563,17 @@ def main():
 
     cfg, bias, beta, levels, local, owned = workload(world, rank)
     E, topk, H, I = cfg["E"], cfg["topk"], cfg["H"], cfg["I"]
-    L, experts = synth.build_layer(cfg, local, seed=SEED, dev=dev, Bmax=4, owned=owned)
+    # Decode at N > 1: every expert is cut along its intermediate dimension (rank r holds columns [r I / N, (r + 1) I / N) of
+    # gate and up and the matching input columns of down, as the reference's serving shards do, sm120/nqload.py:1-4), so a
+    # 1-token call gives every rank 1 / N of every activated expert whatever the routing; the partial outputs are summed
+    # inside the layer kernel.  NQ_DECODE_TP=0: experts split by id instead (a rank works on the picks it owns).  The
+    # prefill and the layer stack below always split the experts by id.
+    tp_decode = world > 1 and os.environ.get("NQ_DECODE_TP", "1") != "0" and I % (128 * world) == 0
+    I_dec, lev_dec = (I // world, levels) if tp_decode else (I, local)
+    if tp_decode:
+        L, experts = synth.build_layer(dict(cfg, I=I_dec), levels, seed=SEED + 7919 * (rank + 1), dev=dev, Bmax=4)
+    else:
+        L, experts = synth.build_layer(cfg, local, seed=SEED, dev=dev, Bmax=4, owned=owned)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
@@ -546,6 +595,9 @@ def main():
         # (or, with NQ_EP_PEER_DECODE=1, a barrier kernel + a sum kernel)
         epd = EPLayer(L, rank, world, peer_rows=64, peer_decode=os.environ.get("NQ_EP_PEER_DECODE", "0") == "1",
                       fused_decode=os.environ.get("NQ_EP_FUSED_DECODE", "1") != "0")
+        tp_par = tp_parity_case(rank, world, dev) if tp_decode else None
+        if tp_par is not None and not tp_par["ok"]:
+            raise SystemExit(f"bench.py: the tensor-parallel decode does not match the sum of its shards: {tp_par}")
 
     def decode_case(B, steps, warmup, seed_off, want_kernel, want_e2e):
         """B tokens per step; returns dict(us_total, bytes_total, [k_us, k_bytes], [e2e_us], clocks)"""
@@ -555,9 +607,9 @@ def main():
             sel, rw = synth.routing(B, E, topk, SEED + seed_off + step, bias, beta)
             sel_h.append(sel); rw_h.append(rw)
             sels.append(sel.to(dev)); rws.append(rw.to(dev)); xs.append(synth.tokens(B, H, SEED + seed_off + 7000 + step))
-            act = [e for e in set(sel.reshape(-1).tolist()) if local[e] > 0]
-            nbytes.append(sum(experts[e].bytes(local[e]) + (3 * H + 3 * I) * 2 for e in act))
-            nbytes_gu.append(sum(experts[e].gu.nbytes(local[e]) + (2 * H + 2 * I) * 2 for e in act))
+            act = [e for e in set(sel.reshape(-1).tolist()) if lev_dec[e] > 0]
+            nbytes.append(sum(experts[e].bytes(lev_dec[e]) + (3 * H + 3 * I_dec) * 2 for e in act))
+            nbytes_gu.append(sum(experts[e].gu.nbytes(lev_dec[e]) + (2 * H + 2 * I_dec) * 2 for e in act))
         xd = [x.to(dev) for x in xs]
 
         def layer(i, x):
@@ -724,7 +776,10 @@ def main():
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": "glm5_moe_layer_decode_1tok", "experts": E, "topk": topk, "hidden": H, "intermediate": I,
                            "level4_experts": N_LEVEL4, "level4_pick_share": round(synth.share_at_level4(levels, bias, beta, E, topk), 3),
-                           "tokens_per_step": 1, "parallelism": f"ep{world}", "l2": "flushed between steps (256 MB write)"},
+                           "tokens_per_step": 1,
+                           "parallelism": (f"tp{world}: every expert cut along its intermediate dimension, partial outputs summed inside the layer kernel"
+                                           if tp_decode else f"ep{world}"),
+                           "l2": "flushed between steps (256 MB write)"},
                 "layer_us": us_total / args.steps, "bytes_per_step": by_total / args.steps,
                 "decode_phases_us": {"kernel_gate_up_alone": r1["gu_us"], "kernel_down_alone": r1["dn_us"],
                                      "nccl_allreduce_alone": r1.get("allreduce_us", 0.0), "partial_outputs_summed_by": r1.get("sum_by", "one GPU: nothing to sum"),
@@ -754,6 +809,7 @@ def main():
                 "decode_32tok_promotion": promo,
                 "layer_stack": stack,
                 "ep_parity": ep_par,
+                "tp_parity": tp_par if world > 1 else None,
                 "clocks": r1["clocks"]}
         if cpu_base is not None:
             line["cpu_baseline"] = cpu_base

@@ -184,18 +184,33 @@ def kperm_order(K):
     return (k - q) + 4 * ((q & 7) >> 1) + 2 * (q >> 3) + (q & 1)
 
 
-def default_ksplit(B, H, I, share=1.0):
-    """k-slices per strip (gate|up, down) for a B-token call: few tokens need more slices to fill 148 SMs.
-    share: fraction of the layer's experts resident on this GPU (expert parallelism: 1 / ranks) - a rank that serves only
-    a few of a token's picks cuts finer."""
-    def pick(chunks, want):
-        for k in (want, 8, 6, 4, 3, 2, 1):
-            if k <= want and chunks % k == 0:
-                return k
-        return 1
-    load = B * share
-    want_gu, want_dn = (8, 4) if load <= 0.5 else (4, 2) if load <= 1 else (2, 1) if load <= 4 else (1, 1)
-    return pick(H // 128, want_gu), pick(I // 128, want_dn)
+def default_ksplit(B, H, I, share=1.0, topk=8):
+    """k-slices per strip (gate|up, down) for a B-token call.  The persistent kernel hands out pieces (a 16-row strip over
+    1 / k-slices of its chunks) to ~3,000 warps: the split aims at ~10 units (16 x 128 weights) per gate|up piece and ~8 per
+    down piece, between 3,000 and 8,192 gate|up pieces and between 1,536 and 6,144 down pieces - what sweeps of the GLM
+    shape and of its tensor-parallel shards (I / 2, I / 4, I / 8) settled on.
+    share: fraction of the layer's experts resident on this GPU (expert parallelism: 1 / ranks; 1 for one GPU and for
+    tensor-parallel shards, whose I is the shard's)."""
+    import math
+    Cg, Cd = H // 128, I // 128
+    if share < 1.0:
+        # expert parallelism: a rank's load swings with the routing (0 .. topk picks of a token), and the call waits for the
+        # fullest rank; the table below is what sweeps with 1 / 2, 1 / 4 and 1 / 8 of the experts resident settled on
+        load = B * share
+        want = (8, 4) if load <= 0.5 else (4, 2) if load <= 1 else (2, 1) if load <= 4 else (1, 1)
+        fit = lambda chunks, w: max(d for d in range(1, w + 1) if chunks % d == 0)
+        return fit(Cg, want[0]), fit(Cd, want[1])
+    runs = max(1.0, B * topk)                              # distinct experts a call activates, roughly
+
+    def nearest(chunks, want):
+        divs = [d for d in range(1, chunks + 1) if chunks % d == 0 and d <= 24]
+        return min(divs, key=lambda d: abs(math.log(d / max(want, 1e-9))))
+
+    per_ks_gu = runs * Cd * 16                             # gate|up pieces per k-slice: strips of gate and up
+    per_ks_dn = runs * Cg * 8                              # down pieces per k-slice
+    want_gu = min(max(per_ks_gu * Cg / 10, 3000), 8192) / per_ks_gu
+    want_dn = min(max(per_ks_dn * Cd / 8, 1536), 6144) / per_ks_dn
+    return nearest(Cg, want_gu), nearest(Cd, want_dn)
 
 
 def moe_workspace(B, topk, H, I, ks_gu, ks_dn):

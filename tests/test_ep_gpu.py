@@ -1,7 +1,8 @@
 """Expert-parallel layer on 2 GPUs (skipped on a single-GPU box): the prefill whose exchange runs over peer memory (input
 rows read from their owners by the first prefill pass, partial rows summed by nq_ep_combine from the peers'
 symmetric-memory buffers, nq_ep_barrier in between) must equal, bit for bit, the all-to-all + indexed-add path, and both
-must match a single-GPU layer holding every expert; decode = replicated tokens + all-reduce.  The exchange kernels and the
+must match a single-GPU layer holding every expert; decode = replicated tokens + all-reduce, with the experts split by id
+or cut along their intermediate dimension (tensor parallel).  The exchange kernels and the
 bounded barrier are also tested on one GPU with emulated ranks."""
 import os
 
@@ -69,6 +70,30 @@ def _worker(rank, world, port, q):
         yb = [ep_bar.decode(xd, seld, rwd).clone() for _ in range(3)]
         torch.cuda.synchronize()
         res["decode_barrier_err"] = max(layer_errors(y.cpu().numpy(), want)[1] for y in yb)
+        # tensor-parallel decode: rank r holds shard r of every expert (I / world columns: an expert of its own), the partial
+        # outputs are summed inside the layer kernel; reference = the shards' layers one after the other on this GPU, in rank
+        # order (bitwise), and the CPU oracle's sum over the shards
+        import numpy as np
+        from oracle import nq_oracle as O
+        from tests.util import expert_to_oracle
+        Is = I // world
+        shards = []
+        for r in range(world):
+            Lr = moe.MoELayer(NE, H, Is, Bmax=4, topk=topk, dev=dev)
+            sx = [moe.Expert(H, Is, seed=900 + 50 * r + i, rk_gu=0, rk_dn=7, var=True, sv=0.02, dev=dev) for i in range(NE)]
+            for e in range(NE):
+                Lr.set(e, sx[e], levels[e])
+            shards.append((Lr, sx))
+        ref_tp = torch.zeros(3, H, dtype=torch.float32, device=dev)
+        for Lr, _ in shards:
+            ref_tp += Lr(xd, seld, rwd)[:3]
+        tp = EPLayer(shards[rank][0], rank, world, peer_rows=world, fused_decode=True)
+        yt = [tp.decode(xd, seld, rwd).clone() for _ in range(3)]
+        torch.cuda.synchronize()
+        res["tp_bitwise"] = all(bool(torch.equal(y, ref_tp)) for y in yt)
+        want_tp = sum(O.moe_ref([expert_to_oracle(e) for e in sx], levels, xd.cpu().numpy(), seld.cpu().numpy(), rwd.cpu().numpy()) for _, sx in shards)
+        res["tp_err"] = layer_errors(yt[0].cpu().numpy(), want_tp.astype(np.float32))[1]
+        res["tp_status"] = shards[rank][0].status() + int(tp.peer is None or tp.peer.timed_out())
         q.put((rank, res))
     finally:
         dist.destroy_process_group()
@@ -92,6 +117,7 @@ def test_prefill_combine_over_peer_memory():
         assert r["same"] and r["err"] <= 1e-4 and r["decode_err"] <= 1e-4 and not r["timed_out"], (rank, r)
         assert r["decode_peer_err"] <= 1e-4 and r["decode_peer_same"] and r["decode_barrier_err"] <= 1e-4, (rank, r)
         assert r["decode_one_sided_err"] <= 1e-4 and r["decode_same_on_all_ranks"] and r["decode_status"] == 0, (rank, r)
+        assert r["tp_bitwise"] and r["tp_err"] <= 1e-4 and r["tp_status"] == 0, (rank, r)
 
 
 def test_exchange_kernels_on_one_gpu():
