@@ -417,6 +417,11 @@ def layer_stack_case(cfg, rank, world, dev, n_layers=16, window=65536):
     layers, eps, keep = [], [], []
     shared_peer = None
     Tl = window // world
+    # the decode step at N > 1 runs on tensor-parallel shards of the same layers (every expert, I / world columns per rank),
+    # as the headline decode case does; NQ_DECODE_TP=0 keeps it on the expert-parallel layers
+    tp_decode = world > 1 and os.environ.get("NQ_DECODE_TP", "1") != "0" and I % (256 * world) == 0
+    Is = I // world
+    tlayers, tps = [], []
     for l in range(n_layers):
         g = torch.Generator().manual_seed(SEED + 900 + l)
         perm = torch.randperm(E, generator=g).tolist()
@@ -439,6 +444,18 @@ def layer_stack_case(cfg, rank, world, dev, n_layers=16, window=65536):
             ep.peer_decode = os.environ.get("NQ_EP_PEER_DECODE", "0") == "1"
             ep.fused_decode = os.environ.get("NQ_EP_FUSED_DECODE", "1") != "0"
             eps.append(ep)
+            if tp_decode:
+                Lt = moe.MoELayer(E, H, Is, nm_gu, Is // 128 // 2, Bmax=1, topk=topk, dev=dev)
+                for e in range(E):
+                    m = kind[e] == 3
+                    ex = moe.Expert(H, Is, seed=((SEED + 31 * l) * 100003 + e) * 8 + rank + 1, nm_gu=nm_gu if m else None,
+                                    nm_dn=Is // 128 // 2 if m else None, dev=dev, rk_gu=0, rk_dn=7, var=True, sv=0.02, gen_device=dev)
+                    keep.append(ex)
+                    Lt.set(e, ex, 2 if kind[e] == 2 else 4)
+                tlayers.append(Lt)
+                tp = EPLayer(Lt, rank, world, peer_rows=0)
+                tp.peer, tp.fused_decode = shared_peer, True
+                tps.append(tp)
     sel, rw = synth.routing(window, E, topk, SEED + 777)
     x = synth.tokens(window, H, SEED + 778)
     sl = slice(rank * Tl, (rank + 1) * Tl)
@@ -497,9 +514,9 @@ def layer_stack_case(cfg, rank, world, dev, n_layers=16, window=65536):
     def decode_step(allreduce=True):
         for l in range(n_layers):
             if world > 1 and allreduce:
-                eps[l].decode(x1, sel1, rw1)
+                (tps if tp_decode else eps)[l].decode(x1, sel1, rw1)
             else:
-                layers[l](x1, sel1, rw1)
+                (tlayers if tp_decode else layers)[l](x1, sel1, rw1)
 
     dt = {}
     for name, ar in (("step", True), ("kernels_only", False)):
@@ -522,7 +539,8 @@ def layer_stack_case(cfg, rank, world, dev, n_layers=16, window=65536):
            "prefill_phases_ms": phases, "prefill_status": status,
            "decode_step_us": dt["step"], "decode_us_per_layer": dt["step"] / n_layers,
            "decode_kernels_only_us": dt["kernels_only"], "decode_allreduce_us": max(dt["step"] - dt["kernels_only"], 0.0) if world > 1 else 0.0,
-           "parallelism": f"ep{world}" + (f", exchange by {eps[0].last_stats.get('dispatch', '?')}" if world > 1 else ""),
+           "parallelism": f"prefill ep{world}" + (f", exchange by {eps[0].last_stats.get('dispatch', '?')}" if world > 1 else "")
+                          + (f"; decode step tp{world} (shards of I / {world} columns)" if tp_decode else ""),
            "plane_gb_per_gpu": sum(e.bytes(4) for e in keep) / 1e9}
     return out
 
