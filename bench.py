@@ -626,8 +626,10 @@ def main():
             sel_h.append(sel); rw_h.append(rw)
             sels.append(sel.to(dev)); rws.append(rw.to(dev)); xs.append(synth.tokens(B, H, SEED + seed_off + 7000 + step))
             act = [e for e in set(sel.reshape(-1).tolist()) if lev_dec[e] > 0]
-            nbytes.append(sum(experts[e].bytes(lev_dec[e]) + (3 * H + 3 * I_dec) * 2 for e in act))
-            nbytes_gu.append(sum(experts[e].gu.nbytes(lev_dec[e]) + (2 * H + 2 * I_dec) * 2 for e in act))
+            # scale vectors of length H are replicated in every tensor-parallel shard: they count once per expert, not per rank
+            h_share = (1.0 / world) if tp_decode else 1.0
+            nbytes.append(sum(experts[e].bytes(lev_dec[e]) + (3 * H * h_share + 3 * I_dec) * 2 for e in act))
+            nbytes_gu.append(sum(experts[e].gu.nbytes(lev_dec[e]) + (2 * H * h_share + 2 * I_dec) * 2 for e in act))
         xd = [x.to(dev) for x in xs]
 
         def layer(i, x):
