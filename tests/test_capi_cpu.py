@@ -82,3 +82,19 @@ def test_generators_are_seeded_and_well_formed():
     assert set(s[:H].abs().tolist()) == {1.0} and float(s[H:H + 2 * I].max()) < 0.2
     e = moe.entry(a, 4)
     assert e[0] == 4 and e[10] == 6 and e[11] == 7 and e[1] == a.gu.base.data_ptr() and e[18] == 0 and e[19] == 0
+
+
+def test_default_ksplit_divides_the_chunks_for_every_shape():
+    """the k-split rule of the decode call: both numbers divide the chunk counts (a workspace can be sized for them) for the
+    GLM shape, its tensor-parallel shards, small test shapes and expert-parallel shares; the tuned points stay put"""
+    from nestquant_b200 import ext
+    for H in (128, 1024, 4096, 6144, 8192):
+        for I in (128, 256, 512, 1024, 1536, 2048, 8192):
+            for B in (1, 2, 3, 4, 8, 16, 32):
+                for share in (1.0, 0.5, 0.25, 0.125):
+                    for topk in (1, 4, 8):
+                        g, d = ext.default_ksplit(B, H, I, share, topk)
+                        assert 1 <= g <= 24 and 1 <= d <= 24 and (H // 128) % g == 0 and (I // 128) % d == 0, (B, H, I, share, topk, g, d)
+    assert ext.default_ksplit(1, 6144, 2048) == (4, 2) and ext.default_ksplit(2, 6144, 2048) == (2, 1)
+    assert ext.default_ksplit(32, 6144, 2048) == (1, 1) and ext.default_ksplit(1, 6144, 256) == (12, 1)
+    assert ext.default_ksplit(1, 6144, 2048, 0.125) == (8, 4)
