@@ -186,9 +186,9 @@ def kperm_order(K):
 
 def default_ksplit(B, H, I, share=1.0, topk=8):
     """k-slices per strip (gate|up, down) for a B-token call.  The persistent kernel hands out pieces (a 16-row strip over
-    1 / k-slices of its chunks) to ~3,000 warps: the split aims at ~10 units (16 x 128 weights) per gate|up piece and ~8 per
-    down piece, between 3,000 and 8,192 gate|up pieces and between 1,536 and 6,144 down pieces - what sweeps of the GLM
-    shape and of its tensor-parallel shards (I / 2, I / 4, I / 8) settled on.
+    1 / k-slices of its chunks) to ~3,000 warps: the split aims at ~8 units (16 x 128 weights) per piece, between 3,000
+    and 8,192 gate|up pieces and between 1,536 and 6,144 down pieces - what sweeps of the GLM shape and of its
+    tensor-parallel shards (I / 2, I / 4, I / 8) at 1, 2 and 4 tokens settled on.
     share: fraction of the layer's experts resident on this GPU (expert parallelism: 1 / ranks; 1 for one GPU and for
     tensor-parallel shards, whose I is the shard's)."""
     import math
@@ -208,7 +208,7 @@ def default_ksplit(B, H, I, share=1.0, topk=8):
 
     per_ks_gu = runs * Cd * 16                             # gate|up pieces per k-slice: strips of gate and up
     per_ks_dn = runs * Cg * 8                              # down pieces per k-slice
-    want_gu = min(max(per_ks_gu * Cg / 10, 3000), 8192) / per_ks_gu
+    want_gu = min(max(per_ks_gu * Cg / 8, 3000), 8192) / per_ks_gu
     want_dn = min(max(per_ks_dn * Cd / 8, 1536), 6144) / per_ks_dn
     return nearest(Cg, want_gu), nearest(Cd, want_dn)
 
