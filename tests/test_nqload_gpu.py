@@ -40,10 +40,10 @@ def test_kernel_decode_equals_encoder_side_decoder(E):
         assert hashlib.sha256(dn.tobytes()).hexdigest() == str(G[f"{tag}.Q{lv}.dn.sha"])
 
 
-@pytest.mark.parametrize("L,levels", [(3, {0: 2, 3: 4}), (3, {0: 4, 3: 2}), (4, {1: 4}), (4, {1: 2})])
-def test_loaded_layer_decode_and_prefill_against_oracle(L, levels):
+@pytest.mark.parametrize("L,tp,levels", [(3, 8, {0: 2, 3: 4}), (3, 8, {0: 4, 3: 2}), (3, 4, {0: 4, 3: 4}), (4, 8, {1: 4}), (4, 8, {1: 2})])
+def test_loaded_layer_decode_and_prefill_against_oracle(L, tp, levels):
     from nestquant_b200 import moe, nqload
-    RL = nqload.RankLayer(ROOT, L, 0, tp=8, dev="cuda")
+    RL = nqload.RankLayer(ROOT, L, 0, tp=tp, dev="cuda")          # tp 4: a group of two shards (I 512)
     E, topk = 4, 2
     M = moe.MoELayer(E, RL.H, RL.I, Bmax=4, topk=topk)
     exs_o, lv = [None] * E, [0] * E
