@@ -94,6 +94,32 @@ def _worker(rank, world, port, q):
         want_tp = sum(O.moe_ref([expert_to_oracle(e) for e in sx], levels, xd.cpu().numpy(), seld.cpu().numpy(), rwd.cpu().numpy()) for _, sx in shards)
         res["tp_err"] = layer_errors(yt[0].cpu().numpy(), want_tp.astype(np.float32))[1]
         res["tp_status"] = shards[rank][0].status() + int(tp.peer is None or tp.peer.timed_out())
+        # the same with production shards: rank r loads shard r of the nestquant-v1 fixture layer (tp 8 layout), the two ranks'
+        # partial outputs are summed in the kernel; reference = the oracle on both shards
+        from nestquant_b200 import nqload
+        root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "nqload")
+        lv3 = {0: 4, 3: 2}
+        RL = nqload.RankLayer(root, 3, rank, tp=8, dev=dev)
+        Ln = moe.MoELayer(4, RL.H, RL.I, Bmax=4, topk=2, dev=dev)
+        for e, ex in RL.ex.items():
+            ex.signs = ex.sc[lv3[e]]
+            Ln.set(e, ex, lv3[e])
+        xn = torch.randn(3, RL.H, generator=g).half().to(dev)
+        seln = torch.tensor([[0, 3], [3, 0], [0, 2]]).to(dev)                   # expert 2 is not in the layer
+        rwn = torch.tensor([[0.6, 0.4], [0.5, 0.5], [1.0, 0.7]]).half().to(dev)
+        tpn = EPLayer(Ln, rank, world, peer_rows=world, fused_decode=True)
+        yn = tpn.decode(xn, seln, rwn).clone()
+        torch.cuda.synchronize()
+        want_n = 0
+        for r in range(world):
+            shard = nqload.RankLayer(root, 3, r, tp=8, dev="cpu")
+            exs_o, lv_o = [None] * 4, [0] * 4
+            for e, ex in shard.ex.items():
+                ex.signs = ex.sc[lv3[e]]
+                exs_o[e], lv_o[e] = expert_to_oracle(ex), lv3[e]
+            want_n = want_n + O.moe_ref(exs_o, lv_o, xn.cpu().numpy(), seln.cpu().numpy(), rwn.cpu().numpy())
+        res["shards_err"] = layer_errors(yn.cpu().numpy(), want_n.astype(np.float32))[1]
+        res["shards_status"] = Ln.status() + int(tpn.peer is None or tpn.peer.timed_out())
         q.put((rank, res))
     finally:
         dist.destroy_process_group()
@@ -118,6 +144,7 @@ def test_prefill_combine_over_peer_memory():
         assert r["decode_peer_err"] <= 1e-4 and r["decode_peer_same"] and r["decode_barrier_err"] <= 1e-4, (rank, r)
         assert r["decode_one_sided_err"] <= 1e-4 and r["decode_same_on_all_ranks"] and r["decode_status"] == 0, (rank, r)
         assert r["tp_bitwise"] and r["tp_err"] <= 1e-4 and r["tp_status"] == 0, (rank, r)
+        assert r["shards_err"] <= 1e-4 and r["shards_status"] == 0, (rank, r)
 
 
 def test_exchange_kernels_on_one_gpu():
