@@ -392,10 +392,12 @@ def tp_parity_case(rank, world, dev):
     y2 = tp.decode(x, sel, rw).clone()
     torch.cuda.synchronize()
     err = torch.tensor([layer_errors(y.cpu().numpy(), ref.cpu().numpy())[1], float(not torch.equal(y, y2)),
-                        float(tp.peer is None or tp.peer.timed_out()), float(shards[rank][0].status())], dtype=torch.float64, device=dev)
+                        float(tp.peer is not None and tp.peer.timed_out()), float(shards[rank][0].status()), float(tp.peer is None)],
+                       dtype=torch.float64, device=dev)
     dist.all_reduce(err, op=dist.ReduceOp.MAX)
     e = err.tolist()
-    return {"decode_rel_l2": e[0], "repeatable": e[1] == 0, "no_peer_buffers_or_timed_out": bool(e[2]), "device_status": int(e[3]),
+    return {"decode_rel_l2": e[0], "repeatable": e[1] == 0, "barrier_timed_out": bool(e[2]), "device_status": int(e[3]),
+            "summed_by": "NCCL all-reduce (no peer buffers on this system)" if e[4] else "the layer kernel over peer memory",
             "ok": bool(e[0] <= 2e-3 and e[1] == 0 and e[2] == 0 and e[3] == 0),
             "case": f"{NE} experts, H {H}, I {I} cut into {world} shards, top-{topk}, {B} tokens against the sum of the shards' layers on one GPU"}
 
